@@ -14,7 +14,8 @@
 //                     registers (4 lanes per column, each holding every 4th row), the step's tokens stream through
 //                     shared memory in blocks of 16; a row that starts at position 0 starts from the zero state, any
 //                     other row continues from the state of its line; padding tokens (t >= n_new[b]) change nothing
-//   head_norm_gate    o -> o / rms_head(o) * weight * sigmoid(gate) (unit norm and weight optional): the output side of
+//   head_norm_gate    o -> o / rms_head(o) * weight * sigmoid(gate) (unit norm and weight optional; the gate may also
+//                     be silu(gate)): the output side of
 //                     the recurrent mixer, and the plain output gate of an attention mixer
 //   relu_squared      max(x, 0)^2
 #include "common.cuh"
@@ -352,7 +353,7 @@ int dispatch_scan(const void* proj, long long ld, int q_off, int k_off, int v_of
 template <typename TO, typename T>
 __global__ void head_norm_gate_kernel(const TO* __restrict__ o, const T* __restrict__ gate, long long ld_g, int g_off,
                                       const float* __restrict__ weight, T* __restrict__ out, long long units, int H,
-                                      int Dv, int normalize, float eps) {
+                                      int Dv, int normalize, float eps, int gate_act) {
     const int lane = threadIdx.x & 31;
     const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (unit >= units) return;
@@ -374,7 +375,8 @@ __global__ void head_norm_gate_kernel(const TO* __restrict__ o, const T* __restr
     for (int c = lane; c < Dv; c += 32) {
         float v = ldf(src + c) * r;
         if (weight != nullptr) v *= weight[hd * Dv + c];
-        v *= 1.f / (1.f + expf(-ldf(g + c)));
+        const float z = ldf(g + c);
+        v *= (gate_act == 1 ? z : 1.f) / (1.f + expf(-z));      // 0: sigmoid(z), 1: silu(z) = z * sigmoid(z)
         stf(dst + c, v);
     }
 }
@@ -442,7 +444,7 @@ NXD_API int nxd_mlstm_scan(int dtype, const void* proj, long long ld, int q_off,
 // o_dtype: dtype of o (0 bf16, 1 fp32); dtype: gate and output
 NXD_API int nxd_head_norm_gate(int o_dtype, int dtype, const void* o, const void* gate, long long ld_g, int g_off,
                                const float* weight, void* out, long long N, int H, int Dv, int normalize, float eps,
-                               void* stream) {
+                               int gate_act, void* stream) {
     const long long units = N * H;
     if (units == 0) return 0;
     const int wpb = 8;
@@ -450,13 +452,16 @@ NXD_API int nxd_head_norm_gate(int o_dtype, int dtype, const void* o, const void
     cudaStream_t st = (cudaStream_t)stream;
     if (o_dtype == 1 && dtype == 0)
         head_norm_gate_kernel<float, bf16><<<blocks, wpb * 32, 0, st>>>((const float*)o, (const bf16*)gate, ld_g, g_off,
-                                                                        weight, (bf16*)out, units, H, Dv, normalize, eps);
+                                                                        weight, (bf16*)out, units, H, Dv, normalize, eps,
+                                                                        gate_act);
     else if (o_dtype == 1 && dtype == 1)
         head_norm_gate_kernel<float, float><<<blocks, wpb * 32, 0, st>>>((const float*)o, (const float*)gate, ld_g, g_off,
-                                                                         weight, (float*)out, units, H, Dv, normalize, eps);
+                                                                         weight, (float*)out, units, H, Dv, normalize, eps,
+                                                                         gate_act);
     else if (o_dtype == 0 && dtype == 0)
         head_norm_gate_kernel<bf16, bf16><<<blocks, wpb * 32, 0, st>>>((const bf16*)o, (const bf16*)gate, ld_g, g_off,
-                                                                       weight, (bf16*)out, units, H, Dv, normalize, eps);
+                                                                       weight, (bf16*)out, units, H, Dv, normalize, eps,
+                                                                       gate_act);
     else
         NXD_REQUIRE(false, "head norm / gate: dtypes %d -> %d", o_dtype, dtype);
     NXD_LAUNCH_CHECK();

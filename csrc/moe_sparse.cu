@@ -2,9 +2,12 @@
 // index on the device ("selective loading": only the chosen experts' weights are touched), clamped gated activation,
 // and the weighted combination in fp32.  bf16 or fp32 activations / expert weights; router in fp32.
 //
-//   router        z = Wr h;  s = softmax(z);  choice = s + correction;  the `top` largest choices are taken,
-//                 weight = s * out_scale (not renormalised);  optional second output sigmoid(<w_sg, h>) per token
-//   activation    g = min(gate, limit), u = clamp(up, -limit, limit);  a = g * sigmoid(alpha * g) * (u + 1)
+//   router        z = Wr h (+ logit bias);  s = softmax(z);  choice = s + correction;  the `top` largest choices are taken,
+//                 weight = s * out_scale (not renormalised);  optional second output sigmoid(<w_sg, h>) per token.
+//                 renormalise: the `top` largest LOGITS are taken and the weights are the softmax over the chosen
+//                 logits only (times out_scale)
+//   activation    g = min(gate, limit), u = clamp(up, -limit, limit);  a = g * sigmoid(alpha * g) * (u + up_shift)
+//                 (limit = +inf, alpha = 1, up_shift = 0: plain silu(gate) * up)
 //   expert index >= E means an identity expert: its output is the token's input itself
 // Expert weights are stored [E, in, out] (the layout of the grouped expert layers), gate | up fused on the out dim.
 #include "common.cuh"
@@ -26,10 +29,10 @@ __device__ __forceinline__ void ld2(const bf16* p, float& a, float& b) {
     b = v.y;
 }
 
-__device__ __forceinline__ float glu_act(float g, float u, float limit, float alpha) {
+__device__ __forceinline__ float glu_act(float g, float u, float limit, float alpha, float up_shift) {
     g = fminf(g, limit);
     u = fminf(fmaxf(u, -limit), limit);
-    return g / (1.f + expf(-alpha * g)) * (u + 1.f);
+    return g / (1.f + expf(-alpha * g)) * (u + up_shift);
 }
 
 // ---- router ---------------------------------------------------------------------------------------------------------
@@ -39,7 +42,8 @@ template <typename T>
 __global__ void __launch_bounds__(RT_WARPS * 32)
 moe_router_kernel(const T* __restrict__ h, const float* __restrict__ wr, const float* __restrict__ corr,
                   const float* __restrict__ wsg, int* __restrict__ idx, float* __restrict__ wts,
-                  float* __restrict__ sgate, long long N, int W, int R, int top, float out_scale) {
+                  float* __restrict__ sgate, long long N, int W, int R, int top, float out_scale,
+                  const float* __restrict__ zbias, int renorm) {
     extern __shared__ float smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     float* ps = smem + (long long)warp * 2 * R;     // probabilities
@@ -60,7 +64,7 @@ moe_router_kernel(const T* __restrict__ h, const float* __restrict__ wr, const f
 #pragma unroll
         for (int i = 0; i < RT_GROUP; ++i) {
             const float z = warp_sum(acc[i]);
-            if (lane == 0 && r0 + i < R) ps[r0 + i] = z;
+            if (lane == 0 && r0 + i < R) ps[r0 + i] = z + (zbias != nullptr ? zbias[r0 + i] : 0.f);
         }
     }
     if (wsg != nullptr && sgate != nullptr) {
@@ -70,18 +74,22 @@ moe_router_kernel(const T* __restrict__ h, const float* __restrict__ wr, const f
         if (lane == 0) sgate[n] = 1.f / (1.f + expf(-a));
     }
     __syncwarp();
-    float mx = -INFINITY;
-    for (int r = lane; r < R; r += 32) mx = fmaxf(mx, ps[r]);
-    mx = warp_max(mx);
-    float sum = 0.f;
-    for (int r = lane; r < R; r += 32) sum += expf(ps[r] - mx);
-    sum = warp_sum(sum);
-    const float inv = 1.f / sum;
-    __syncwarp();
-    for (int r = lane; r < R; r += 32) {
-        const float p = expf(ps[r] - mx) * inv;
-        ps[r] = p;
-        cs[r] = p + (corr != nullptr ? corr[r] : 0.f);
+    if (renorm) {                // the choice is made on the logits themselves
+        for (int r = lane; r < R; r += 32) cs[r] = ps[r];
+    } else {
+        float mx = -INFINITY;
+        for (int r = lane; r < R; r += 32) mx = fmaxf(mx, ps[r]);
+        mx = warp_max(mx);
+        float sum = 0.f;
+        for (int r = lane; r < R; r += 32) sum += expf(ps[r] - mx);
+        sum = warp_sum(sum);
+        const float inv = 1.f / sum;
+        __syncwarp();
+        for (int r = lane; r < R; r += 32) {
+            const float p = expf(ps[r] - mx) * inv;
+            ps[r] = p;
+            cs[r] = p + (corr != nullptr ? corr[r] : 0.f);
+        }
     }
     __syncwarp();
     for (int k = 0; k < top; ++k) {
@@ -106,10 +114,21 @@ moe_router_kernel(const T* __restrict__ h, const float* __restrict__ wr, const f
         if (bi >= R) bi = 0;      // every score NaN: keep the index in range
         if (lane == 0) {
             idx[n * top + k] = bi;
-            wts[n * top + k] = ps[bi] * out_scale;
+            wts[n * top + k] = renorm ? ps[bi] : ps[bi] * out_scale;
             cs[bi] = -INFINITY;
         }
         __syncwarp();
+    }
+    if (renorm && lane == 0) {   // softmax over the chosen logits only; the first pick is the largest
+        const float mx = wts[n * top];
+        float sum = 0.f;
+        for (int k = 0; k < top; ++k) {
+            const float e = expf(wts[n * top + k] - mx);
+            wts[n * top + k] = e;
+            sum += e;
+        }
+        const float inv = out_scale / sum;
+        for (int k = 0; k < top; ++k) wts[n * top + k] *= inv;
     }
 }
 
@@ -119,7 +138,8 @@ constexpr int GV_WARPS = 8;
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(GV_WARPS * 32)
 moe_gate_up_act_kernel(const T* __restrict__ h, const T* __restrict__ wgu, const int* __restrict__ idx,
-                       T* __restrict__ act, int pairs_per_token, int W, int F, int E, float limit, float alpha) {
+                       T* __restrict__ act, int pairs_per_token, int W, int F, int E, float limit, float alpha,
+                       float up_shift) {
     extern __shared__ float smem[];
     constexpr int PER = VEC ? 2 : 1, COLS = 32 * PER;
     float* hs = smem;                                  // [W]
@@ -172,7 +192,7 @@ moe_gate_up_act_kernel(const T* __restrict__ h, const T* __restrict__ wgu, const
                 g += red[((long long)w * COLS + threadIdx.x) * 2];
                 u += red[((long long)w * COLS + threadIdx.x) * 2 + 1];
             }
-            stf(act + p * F + f, glu_act(g, u, limit, alpha));
+            stf(act + p * F + f, glu_act(g, u, limit, alpha, up_shift));
         }
     }
 }
@@ -260,12 +280,27 @@ moe_down_combine_kernel(const T* __restrict__ act, const T* __restrict__ wd, con
 // ---- pieces of the sorted (GEMM) path: activation over [M, 2F], gather-combine -------------------------------------------
 template <typename T>
 __global__ void clamped_glu_kernel(const T* __restrict__ gu, T* __restrict__ out, long long M, int F, float limit,
-                                   float alpha) {
+                                   float alpha, float up_shift) {
     const long long total = M * F;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const long long m = i / F;
         const int f = (int)(i - m * F);
-        stf(out + i, glu_act(ldf(gu + m * 2 * F + f), ldf(gu + m * 2 * F + F + f), limit, alpha));
+        stf(out + i, glu_act(ldf(gu + m * 2 * F + f), ldf(gu + m * 2 * F + F + f), limit, alpha, up_shift));
+    }
+}
+
+// gate and up are column ranges of a wider row (a fused projection output), each with an optional fp32 bias
+template <typename T>
+__global__ void glu_bias_kernel(const T* __restrict__ src, long long ld, int gate_off, int up_off,
+                                const float* __restrict__ gb, const float* __restrict__ ub, T* __restrict__ out, long long M,
+                                int F, float limit, float alpha, float up_shift) {
+    const long long total = M * F;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long m = i / F;
+        const int f = (int)(i - m * F);
+        const float g = ldf(src + m * ld + gate_off + f) + (gb != nullptr ? gb[f] : 0.f);
+        const float u = ldf(src + m * ld + up_off + f) + (ub != nullptr ? ub[f] : 0.f);
+        stf(out + i, glu_act(g, u, limit, alpha, up_shift));
     }
 }
 
@@ -291,8 +326,10 @@ __global__ void moe_gather_combine_kernel(const T* __restrict__ ys, const int* _
 }  // namespace
 
 // dtype: 0 bf16, 1 fp32 (activations and expert weights).  R = router outputs (experts + identity experts).
+// zbias [R] fp32 or NULL: added to the logits; renorm != 0: choice on the logits, weights = softmax over the chosen ones.
 NXD_API int nxd_moe_router(int dtype, const void* h, const float* wr, const float* corr, const float* wsg, int* idx,
-                           float* wts, float* sgate, long long N, int W, int R, int top, float out_scale, void* stream) {
+                           float* wts, float* sgate, long long N, int W, int R, int top, float out_scale,
+                           const float* zbias, int renorm, void* stream) {
     if (N == 0) return 0;
     NXD_REQUIRE(top >= 1 && top <= R, "router: top %d of %d", top, R);
     const size_t smem = (size_t)RT_WARPS * 2 * R * sizeof(float);
@@ -300,11 +337,12 @@ NXD_API int nxd_moe_router(int dtype, const void* h, const float* wr, const floa
     const unsigned blocks = (unsigned)((N + RT_WARPS - 1) / RT_WARPS);
     if (dtype == 0)
         moe_router_kernel<bf16><<<blocks, RT_WARPS * 32, smem, (cudaStream_t)stream>>>((const bf16*)h, wr, corr, wsg, idx,
-                                                                                      wts, sgate, N, W, R, top, out_scale);
+                                                                                      wts, sgate, N, W, R, top, out_scale,
+                                                                                      zbias, renorm);
     else
         moe_router_kernel<float><<<blocks, RT_WARPS * 32, smem, (cudaStream_t)stream>>>((const float*)h, wr, corr, wsg,
                                                                                        idx, wts, sgate, N, W, R, top,
-                                                                                       out_scale);
+                                                                                       out_scale, zbias, renorm);
     NXD_LAUNCH_CHECK();
     return 0;
 }
@@ -312,7 +350,8 @@ NXD_API int nxd_moe_router(int dtype, const void* h, const float* wr, const floa
 // act[p, :] = activation(h[p / pairs_per_token] @ wgu[idx[p]]) for P pairs; idx NULL = expert 0 for every pair (a dense
 // gated MLP); pairs whose index is outside [0, E) are identity experts and are skipped.
 NXD_API int nxd_moe_gate_up_act(int dtype, const void* h, const void* wgu, const int* idx, void* act, long long P,
-                                int pairs_per_token, int W, int F, int E, float limit, float alpha, void* stream) {
+                                int pairs_per_token, int W, int F, int E, float limit, float alpha, float up_shift,
+                                void* stream) {
     if (P == 0) return 0;
     NXD_REQUIRE(P < (1ll << 31), "gate/up: %lld pairs", P);
     const bool vec = (F % 2) == 0;
@@ -327,7 +366,7 @@ NXD_API int nxd_moe_gate_up_act(int dtype, const void* h, const void* wgu, const
         if (smem > 48 * 1024)                                                                                         \
             NXD_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));       \
         kern<<<grid, GV_WARPS * 32, smem, st>>>((const T*)h, (const T*)wgu, idx, (T*)act, pairs_per_token, W, F, E,   \
-                                                limit, alpha);                                                        \
+                                                limit, alpha, up_shift);                                              \
     } while (0)
     if (dtype == 0) {
         if (vec) NXD_GU(bf16, true); else NXD_GU(bf16, false);
@@ -365,17 +404,17 @@ NXD_API int nxd_moe_down_combine(int dtype, const void* act, const void* wd, con
 }
 
 NXD_API int nxd_clamped_glu(int dtype, const void* gate_up, void* out, long long M, int F, float limit, float alpha,
-                            void* stream) {
+                            float up_shift, void* stream) {
     if (M == 0) return 0;
     long long blocks = (M * F + 255) / 256;
     const long long cap = (long long)nxd_num_sms() * 16;
     if (blocks > cap) blocks = cap;
     if (dtype == 0)
         clamped_glu_kernel<bf16><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((const bf16*)gate_up, (bf16*)out, M, F,
-                                                                                    limit, alpha);
+                                                                                    limit, alpha, up_shift);
     else
         clamped_glu_kernel<float><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((const float*)gate_up, (float*)out, M,
-                                                                                     F, limit, alpha);
+                                                                                     F, limit, alpha, up_shift);
     NXD_LAUNCH_CHECK();
     return 0;
 }
@@ -392,6 +431,25 @@ NXD_API int nxd_moe_gather_combine(int dtype, const void* ys, const int* slot, c
     else
         moe_gather_combine_kernel<float><<<(unsigned)N, 128, 0, (cudaStream_t)stream>>>(
             (const float*)ys, slot, idx, wts, (const float*)h, (const float*)shared_out, sgate, y, top, W, E);
+    NXD_LAUNCH_CHECK();
+    return 0;
+}
+
+NXD_API int nxd_glu_bias(int dtype, const void* src, long long ld, int gate_off, int up_off, const float* gate_bias,
+                         const float* up_bias, void* out, long long M, int F, float limit, float alpha, float up_shift,
+                         void* stream) {
+    if (M * F == 0) return 0;
+    long long blocks = (M * F + 255) / 256;
+    const long long cap = (long long)nxd_num_sms() * 16;
+    if (blocks > cap) blocks = cap;
+    if (dtype == 0)
+        glu_bias_kernel<bf16><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((const bf16*)src, ld, gate_off, up_off,
+                                                                                 gate_bias, up_bias, (bf16*)out, M, F, limit,
+                                                                                 alpha, up_shift);
+    else
+        glu_bias_kernel<float><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((const float*)src, ld, gate_off, up_off,
+                                                                                  gate_bias, up_bias, (float*)out, M, F,
+                                                                                  limit, alpha, up_shift);
     NXD_LAUNCH_CHECK();
     return 0;
 }

@@ -138,7 +138,85 @@ int launch_chain(const void* y, const float* w_post, float* x, const float* w_ne
     return 0;
 }
 
+// Parallel sublayers with layer scale and a gated residual, and the next layer's norm, in one pass over the fp32 stream:
+//
+//   x <- x + ls1 * sigmoid(gate[:, off1 + c] + gb1) * y1  +  ls2 * sigmoid(gate[:, off2 + c] + gb2) * (y2 + y2b)
+//   h  = cast(x / sqrt(mean(x^2) + eps) * w_next[0])            (the norm's weight is ONE number)
+//
+// y1 == NULL: no update (the plain norm of the stream); y2 == NULL: one sublayer; w_next == NULL: no h.
+__device__ __forceinline__ float ld_any(const void* p, int is_f32, long long i) {
+    return is_f32 ? reinterpret_cast<const float*>(p)[i] : __bfloat162float(reinterpret_cast<const bf16*>(p)[i]);
+}
+
+template <typename TH>
+__global__ void __launch_bounds__(PN_THREADS)
+gated_residual_norm_kernel(float* __restrict__ x, const void* __restrict__ y1, int y1_f32, const void* __restrict__ y2,
+                           int y2_f32, const float* __restrict__ y2_bias, const void* __restrict__ gate, int gate_f32,
+                           long long ld_g, int off1, int off2, const float* __restrict__ gb1,
+                           const float* __restrict__ gb2, const float* __restrict__ ls1, const float* __restrict__ ls2,
+                           const float* __restrict__ w_next, TH* __restrict__ h, int W, float eps) {
+    extern __shared__ float rowbuf[];
+    __shared__ float red[32];
+    const long long row = blockIdx.x;
+    float* xr = x + row * W;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < W; c += PN_THREADS) {
+        float v = xr[c];
+        if (y1 != nullptr) {
+            float z = gate != nullptr ? ld_any(gate, gate_f32, row * ld_g + off1 + c) + (gb1 != nullptr ? gb1[c] : 0.f) : 0.f;
+            float a = ld_any(y1, y1_f32, row * W + c) * (ls1 != nullptr ? ls1[c] : 1.f);
+            if (gate != nullptr) a *= 1.f / (1.f + expf(-z));
+            if (y2 != nullptr) {
+                float f = (ld_any(y2, y2_f32, row * W + c) + (y2_bias != nullptr ? y2_bias[c] : 0.f)) *
+                          (ls2 != nullptr ? ls2[c] : 1.f);
+                if (gate != nullptr) {
+                    z = ld_any(gate, gate_f32, row * ld_g + off2 + c) + (gb2 != nullptr ? gb2[c] : 0.f);
+                    f *= 1.f / (1.f + expf(-z));
+                }
+                a += f;
+            }
+            v += a;
+            xr[c] = v;
+        }
+        rowbuf[c] = v;
+        ss = fmaf(v, v, ss);
+    }
+    if (w_next == nullptr || h == nullptr) return;
+    const float r = w_next[0] / sqrtf(block_sum(ss, red) / (float)W + eps);
+    TH* hr = h + row * W;
+    for (int c = threadIdx.x; c < W; c += PN_THREADS) stf(hr + c, rowbuf[c] * r);
+}
+
 }  // namespace
+
+// x [rows, W] fp32 stream, updated in place when y1 is given.  y1, y2 [rows, W] (dtype codes 0 bf16 / 1 fp32; y2 may be
+// NULL), y2_bias [W] fp32 or NULL.  gate [rows, ld_g] (gate_dtype) or NULL: the residual gates' pre-activations at
+// columns off1 (for y1) and off2 (for y2), gb1 / gb2 [W] fp32 their biases (or NULL); ls1 / ls2 [W] fp32 layer scales
+// (or NULL).  w_next: pointer to the ONE fp32 weight of the following norm (or NULL); h [rows, W] (h_dtype) or NULL.
+NXD_API int nxd_gated_residual_norm(float* x, const void* y1, int y1_dtype, const void* y2, int y2_dtype,
+                                    const float* y2_bias, const void* gate, int gate_dtype, long long ld_g, int off1,
+                                    int off2, const float* gb1, const float* gb2, const float* ls1, const float* ls2,
+                                    const float* w_next, void* h, int h_dtype, long long rows, int W, float eps,
+                                    void* stream) {
+    if (rows == 0) return 0;
+    NXD_REQUIRE(rows < (1ll << 31), "gated residual: %lld rows", rows);
+    const size_t smem = (size_t)W * sizeof(float);
+    NXD_REQUIRE(smem <= 200 * 1024, "gated residual: width %d", W);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (h_dtype == 0) {
+        auto kern = gated_residual_norm_kernel<bf16>;
+        if (smem > 48 * 1024) NXD_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        kern<<<(unsigned)rows, PN_THREADS, smem, st>>>(x, y1, y1_dtype, y2, y2_dtype, y2_bias, gate, gate_dtype, ld_g, off1,
+                                                       off2, gb1, gb2, ls1, ls2, w_next, (bf16*)h, W, eps);
+    } else {
+        auto kern = gated_residual_norm_kernel<float>;
+        if (smem > 48 * 1024) NXD_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        kern<<<(unsigned)rows, PN_THREADS, smem, st>>>(x, y1, y1_dtype, y2, y2_dtype, y2_bias, gate, gate_dtype, ld_g, off1,
+                                                       off2, gb1, gb2, ls1, ls2, w_next, (float*)h, W, eps);
+    }
+    NXD_LAUNCH_CHECK();
+    return 0;
+}
 
 // y [rows, W] (y_dtype), w [W] (w_dtype), x [rows, W] fp32 or NULL, h [rows, W] (h_dtype) or NULL; dtypes: 0 bf16,
 // 1 fp32.  offset is added to the weight (1 for a weight stored around zero, 0 for a plain weight).

@@ -29,7 +29,9 @@ struct CacheAddr {
     long long stride_line, stride_head;   // elements
     const int* block_table;
     int page_size, table_cols, row_dim;
+    int head_mod;                         // > 0: head g reads head g % head_mod (value heads shared by groups of key heads)
     __device__ __forceinline__ long long row(int line, int g, int pos) const {
+        if (head_mod > 0) g %= head_mod;
         if (block_table != nullptr) {
             const int page = block_table[(long long)line * table_cols + pos / page_size];
             return (long long)page * stride_line + (long long)g * stride_head + (long long)(pos % page_size) * row_dim;
@@ -52,11 +54,11 @@ __global__ void qk_norm_cache_write_kernel(const T* __restrict__ qkv, long long 
                                            int Dv, int has_kv, int normalize, float eps, int max_pos, int writeback,
                                            const float* __restrict__ q_weight, const float* __restrict__ k_weight,
                                            const float* __restrict__ rope_cos, const float* __restrict__ rope_sin,
-                                           int rope_dims, int value_from_key) {
+                                           int rope_dims, int value_from_key, int Gv) {
     const int lane = threadIdx.x & 31;
     const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (unit >= units) return;
-    const int per_row = H + (has_kv ? 2 * G : 0);
+    const int per_row = H + (has_kv ? G + Gv : 0);
     const long long n = unit / per_row;
     const int hd = (int)(unit % per_row);
     const int b = (int)(n / Tn), t = (int)(n % Tn);
@@ -827,9 +829,40 @@ int launch_decode_mma(const void* q, const void* ck, const void* cv, CacheAddr k
     return 0;
 }
 
+// maps [N, 2H, Dv]: heads 0 .. H-1 are the first attention map, H .. 2H-1 the second (same values).  One warp per
+// (token, head): o = a1 - lambda a2 in fp32, divided by its root mean square over Dv, times (1 - diff).
+template <typename T>
+__global__ void diff_attn_combine_kernel(const T* __restrict__ maps, T* __restrict__ out, const float* __restrict__ lq1,
+                                         const float* __restrict__ lk1, const float* __restrict__ lq2,
+                                         const float* __restrict__ lk2, long long units, int H, int Dv, int D, float diff,
+                                         float eps) {
+    const int lane = threadIdx.x & 31;
+    const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (unit >= units) return;
+    float s1 = 0.f, s2 = 0.f;
+    for (int i = lane; i < D; i += 32) {
+        s1 = fmaf(lq1[i], lk1[i], s1);
+        s2 = fmaf(lq2[i], lk2[i], s2);
+    }
+    const float lambda = expf(warp_sum(s1)) - expf(warp_sum(s2)) + diff;
+    const long long n = unit / H;
+    const int hd = (int)(unit % H);
+    const T* a1 = maps + (n * 2 * H + hd) * Dv;
+    const T* a2 = a1 + (long long)H * Dv;
+    float ss = 0.f;
+    for (int c = lane; c < Dv; c += 32) {
+        const float o = ldf(a1 + c) - lambda * ldf(a2 + c);
+        ss = fmaf(o, o, ss);
+    }
+    const float r = (1.f - diff) / sqrtf(warp_sum(ss) / (float)Dv + eps);
+    T* dst = out + unit * Dv;
+    for (int c = lane; c < Dv; c += 32) stf(dst + c, (ldf(a1 + c) - lambda * ldf(a2 + c)) * r);
+}
+
 CacheAddr make_addr(long long stride_line, long long stride_head, const int* block_table, int page_size, int table_cols,
-                    int row_dim) {
+                    int row_dim, int head_mod = 0) {
     CacheAddr a;
+    a.head_mod = head_mod;
     a.stride_line = stride_line;
     a.stride_head = stride_head;
     a.block_table = block_table;
@@ -896,9 +929,12 @@ NXD_API int nxd_qk_prep_cache_write(int dtype, const void* qkv, long long ld, vo
                                     const int* q_start, const int* n_new, const int* seq_ids, int B, int Tn, int H, int G,
                                     int D, int Dv, int has_kv, int normalize, float eps, int max_pos, int writeback,
                                     const float* q_weight, const float* k_weight, const float* rope_cos,
-                                    const float* rope_sin, int rope_dims, int value_from_key, void* stream) {
-    const long long units = (long long)B * Tn * (H + (has_kv ? 2 * G : 0));
+                                    const float* rope_sin, int rope_dims, int value_from_key, int value_heads,
+                                    void* stream) {
+    const int Gv = value_heads > 0 ? value_heads : G;
+    const long long units = (long long)B * Tn * (H + (has_kv ? G + Gv : 0));
     if (units == 0) return 0;
+    NXD_REQUIRE(!value_from_key || Gv == G, "values taken from the keys need as many value heads (%d) as key heads (%d)", Gv, G);
     NXD_REQUIRE(rope_cos == nullptr || (rope_dims % 2 == 0 && rope_dims <= D), "rotation over %d of %d dimensions", rope_dims, D);
     NXD_REQUIRE(!value_from_key || Dv == D, "values taken from the keys need equal sizes (%d, %d)", D, Dv);
     NXD_REQUIRE(!(writeback && rope_cos != nullptr), "write-back of rotated keys is not %s", "supported");
@@ -910,12 +946,12 @@ NXD_API int nxd_qk_prep_cache_write(int dtype, const void* qkv, long long ld, vo
         qk_norm_cache_write_kernel<bf16><<<blocks, wpb * 32, 0, (cudaStream_t)stream>>>(
             (const bf16*)qkv, ld, (bf16*)q_out, (bf16*)cache_k, (bf16*)cache_v, ka, va, q_start, n_new, seq_ids, units, Tn,
             H, G, D, Dv, has_kv, normalize, eps, max_pos, writeback, q_weight, k_weight, rope_cos, rope_sin, rope_dims,
-            value_from_key);
+            value_from_key, Gv);
     else
         qk_norm_cache_write_kernel<float><<<blocks, wpb * 32, 0, (cudaStream_t)stream>>>(
             (const float*)qkv, ld, (float*)q_out, (float*)cache_k, (float*)cache_v, ka, va, q_start, n_new, seq_ids, units,
             Tn, H, G, D, Dv, has_kv, normalize, eps, max_pos, writeback, q_weight, k_weight, rope_cos, rope_sin, rope_dims,
-            value_from_key);
+            value_from_key, Gv);
     NXD_LAUNCH_CHECK();
     return 0;
 }
@@ -929,7 +965,7 @@ NXD_API int nxd_qk_norm_cache_write(int dtype, const void* qkv, long long ld, vo
     return nxd_qk_prep_cache_write(dtype, qkv, ld, q_out, cache_k, cache_v, k_stride_line, k_stride_head, v_stride_line,
                                    v_stride_head, block_table, page_size, table_cols, q_start, n_new, seq_ids, B, Tn, H, G,
                                    D, Dv, has_kv, normalize, eps, max_pos, writeback, nullptr, nullptr, nullptr, nullptr, 0,
-                                   0, stream);
+                                   0, 0, stream);
 }
 
 // q [B, Tn, H, D] -> out [B, Tn, H, Dv]; the keys and values of positions [0, q_start[b] + n_new[b]) are read from the
@@ -943,12 +979,13 @@ NXD_API int nxd_masked_attn_prefill(int dtype, const void* q, const void* cache_
                                     const int* block_table, int page_size, int table_cols, void* out, const int* q_start,
                                     const int* n_new, const int* seq_ids, const float* slopes, const float* sinks, int B,
                                     int Tn, int H, int G, int D, int Dv, float scale, int window, int keep_first, int chunk,
-                                    int impl, void* stream) {
+                                    int impl, int value_heads, void* stream) {
     NXD_REQUIRE(G > 0 && H % G == 0, "attention: %d query heads over %d key/value heads", H, G);
     NXD_REQUIRE(Dv <= MAXC * 8, "attention: value size %d above %d", Dv, MAXC * 8);
     if (B * Tn == 0) return 0;
+    const int vmod = (value_heads > 0 && value_heads < G) ? value_heads : 0;
     const CacheAddr ka = make_addr(k_stride_line, k_stride_head, block_table, page_size, table_cols, (int)k_row);
-    const CacheAddr va = make_addr(v_stride_line, v_stride_head, block_table, page_size, table_cols, (int)v_row);
+    const CacheAddr va = make_addr(v_stride_line, v_stride_head, block_table, page_size, table_cols, (int)v_row, vmod);
     cudaStream_t st = (cudaStream_t)stream;
     // bf16 with head sizes the tensor-core kernel is compiled for (cache rows must start on 16-byte boundaries);
     // everything else takes the generic kernel
@@ -985,7 +1022,7 @@ NXD_API int nxd_window_attn_prefill(int dtype, const void* q, const void* cache_
                                     int window, int keep_first, int impl, void* stream) {
     return nxd_masked_attn_prefill(dtype, q, cache_k, cache_v, k_stride_line, k_stride_head, D, v_stride_line,
                                    v_stride_head, Dv, block_table, page_size, table_cols, out, q_start, n_new, seq_ids,
-                                   slopes, nullptr, B, Tn, H, G, D, Dv, scale, window, keep_first, 0, impl, stream);
+                                   slopes, nullptr, B, Tn, H, G, D, Dv, scale, window, keep_first, 0, impl, 0, stream);
 }
 
 // q [B, H, D] of one new token per row at positions[b] (its key and value already in the cache) -> out [B, H, Dv].
@@ -994,12 +1031,14 @@ NXD_API int nxd_masked_attn_decode(int dtype, const void* q, const void* cache_k
                                    long long v_stride_line, long long v_stride_head, long long v_row,
                                    const int* block_table, int page_size, int table_cols, void* out, const int* positions,
                                    const int* seq_ids, const float* slopes, const float* sinks, int B, int H, int G, int D,
-                                   int Dv, float scale, int window, int keep_first, int chunk, int impl, void* stream) {
+                                   int Dv, float scale, int window, int keep_first, int chunk, int impl, int value_heads,
+                                   void* stream) {
     NXD_REQUIRE(G > 0 && H % G == 0, "attention: %d query heads over %d key/value heads", H, G);
     NXD_REQUIRE(Dv <= 512, "attention: value size %d above %d", Dv, 512);
     if (B == 0) return 0;
+    const int vmod = (value_heads > 0 && value_heads < G) ? value_heads : 0;
     const CacheAddr ka = make_addr(k_stride_line, k_stride_head, block_table, page_size, table_cols, (int)k_row);
-    const CacheAddr va = make_addr(v_stride_line, v_stride_head, block_table, page_size, table_cols, (int)v_row);
+    const CacheAddr va = make_addr(v_stride_line, v_stride_head, block_table, page_size, table_cols, (int)v_row, vmod);
     cudaStream_t st = (cudaStream_t)stream;
     if (dtype == 0 && impl != 1 && (k_stride_head % 8) == 0 && (v_stride_head % 8) == 0 && (k_stride_line % 8) == 0 &&
         (v_stride_line % 8) == 0 && (k_row % 8) == 0 && (v_row % 8) == 0 && ((uintptr_t)cache_k % 16) == 0 &&
@@ -1038,5 +1077,23 @@ NXD_API int nxd_window_attn_decode(int dtype, const void* q, const void* cache_k
                                    int G, int D, int Dv, float scale, int window, int keep_first, int impl, void* stream) {
     return nxd_masked_attn_decode(dtype, q, cache_k, cache_v, k_stride_line, k_stride_head, D, v_stride_line,
                                   v_stride_head, Dv, block_table, page_size, table_cols, out, positions, seq_ids, slopes,
-                                  nullptr, B, H, G, D, Dv, scale, window, keep_first, 0, impl, stream);
+                                  nullptr, B, H, G, D, Dv, scale, window, keep_first, 0, impl, 0, stream);
+}
+
+NXD_API int nxd_diff_attn_combine(int dtype, const void* maps, void* out, const float* lq1, const float* lk1,
+                                  const float* lq2, const float* lk2, long long N, int H, int Dv, int D, float diff,
+                                  float eps, void* stream) {
+    const long long units = N * H;
+    if (units == 0) return 0;
+    const int wpb = 8;
+    const unsigned blocks = (unsigned)((units + wpb - 1) / wpb);
+    if (dtype == 0)
+        diff_attn_combine_kernel<bf16><<<blocks, wpb * 32, 0, (cudaStream_t)stream>>>((const bf16*)maps, (bf16*)out, lq1, lk1,
+                                                                                     lq2, lk2, units, H, Dv, D, diff, eps);
+    else
+        diff_attn_combine_kernel<float><<<blocks, wpb * 32, 0, (cudaStream_t)stream>>>((const float*)maps, (float*)out, lq1,
+                                                                                      lk1, lq2, lk2, units, H, Dv, D, diff,
+                                                                                      eps);
+    NXD_LAUNCH_CHECK();
+    return 0;
 }

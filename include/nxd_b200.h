@@ -311,19 +311,25 @@ int nxd_qk_prep_cache_write(int dtype, const void* qkv, long long ld, void* q_ou
                             const int* q_start, const int* n_new, const int* seq_ids, int B, int Tn, int H, int G, int D,
                             int Dv, int has_kv, int normalize, float eps, int max_pos, int writeback,
                             const float* q_weight, const float* k_weight, const float* rope_cos, const float* rope_sin,
-                            int rope_dims, int value_from_key, void* stream);
+                            int rope_dims, int value_from_key, int value_heads, void* stream);
+/* value_heads (0 = as many as key heads): head g of the value cache serves the key heads g, g + value_heads, ...
+ * (several attention maps over the same values); the projection row then holds value_heads value heads. */
 int nxd_masked_attn_prefill(int dtype, const void* q, const void* cache_k, const void* cache_v, long long k_stride_line,
                             long long k_stride_head, long long k_row, long long v_stride_line, long long v_stride_head,
                             long long v_row, const int* block_table, int page_size, int table_cols, void* out,
                             const int* q_start, const int* n_new, const int* seq_ids, const float* slopes,
                             const float* sinks, int B, int Tn, int H, int G, int D, int Dv, float scale, int window,
-                            int keep_first, int chunk, int impl, void* stream);
+                            int keep_first, int chunk, int impl, int value_heads, void* stream);
 int nxd_masked_attn_decode(int dtype, const void* q, const void* cache_k, const void* cache_v, long long k_stride_line,
                            long long k_stride_head, long long k_row, long long v_stride_line, long long v_stride_head,
                            long long v_row, const int* block_table, int page_size, int table_cols, void* out,
                            const int* positions, const int* seq_ids, const float* slopes, const float* sinks, int B, int H,
                            int G, int D, int Dv, float scale, int window, int keep_first, int chunk, int impl,
-                           void* stream);
+                           int value_heads, void* stream);
+/* differential attention: maps [N, 2 * H, Dv] (first H heads = map 1, last H = map 2) -> out [N, H * Dv] =
+ * rms_head(a1 - lambda * a2) * (1 - diff), lambda = exp(<lq1, lk1>) - exp(<lq2, lk2>) + diff (vectors fp32 [D]) */
+int nxd_diff_attn_combine(int dtype, const void* maps, void* out, const float* lq1, const float* lk1, const float* lq2,
+                          const float* lk2, long long N, int H, int Dv, int D, float diff, float eps, void* stream);
 /* latent attention: un-rotated query columns -> q_nope, rotated query columns -> q_rot, cache row [norm(c) * w | k_rot] */
 int nxd_latent_prep(int dtype, const void* proj, long long ld, int q_off, int kv_off, void* q_nope, long long nope_head,
                     void* q_rot, long long rot_head, void* cache, long long stride_line, long long row_pitch,
@@ -346,7 +352,8 @@ int nxd_mlstm_scan(int dtype, const void* proj, long long ld, int q_off, int k_o
                    float* out, const int* q_start, const int* n_new, const int* seq_ids, int B, int Tn, int H, int D,
                    int Dv, float qscale, void* stream);
 int nxd_head_norm_gate(int o_dtype, int dtype, const void* o, const void* gate, long long ld_g, int g_off,
-                       const float* weight, void* out, long long N, int H, int Dv, int normalize, float eps, void* stream);
+                       const float* weight, void* out, long long N, int H, int Dv, int normalize, float eps,
+                       int gate_act /* 0 sigmoid, 1 silu */, void* stream);
 int nxd_relu_squared(int dtype, const void* x, void* y, long long n, void* stream);
 /* x (fp32, in place) += norm(y) * w_post (y may be NULL); h (may be NULL) = cast(norm(x) * w_next); center: 1 = layer
  * norm without bias, 0 = RMS norm */
@@ -359,16 +366,42 @@ int nxd_flash_attn_fwd_tc_window(const void* q, const void* k, const void* v, vo
 /* n = y / sqrt(mean(y^2) + eps) * (offset + w);  x (fp32, may be NULL) += n in place;  h (may be NULL) = cast(x or n) */
 int nxd_post_norm_residual(int y_dtype, int w_dtype, int h_dtype, const void* y, const void* w, float* x, void* h,
                            long long rows, int W, float eps, float offset, void* stream);
-/* router: s = softmax(wr h); the `top` largest (s + corr) are chosen, weight = s * out_scale; sgate = sigmoid(<wsg, h>) */
+/* parallel sublayers with layer scale and sigmoid-gated residual on an fp32 stream, then the next norm (one weight):
+ * x += ls1 * sigmoid(gate[off1 + c] + gb1) * y1 + ls2 * sigmoid(gate[off2 + c] + gb2) * (y2 + y2_bias);
+ * h = cast(x / sqrt(mean(x^2) + eps) * w_next[0]).  NULL y1: no update; NULL y2 / gate / w_next: that part is skipped */
+int nxd_gated_residual_norm(float* x, const void* y1, int y1_dtype, const void* y2, int y2_dtype, const float* y2_bias,
+                            const void* gate, int gate_dtype, long long ld_g, int off1, int off2, const float* gb1,
+                            const float* gb2, const float* ls1, const float* ls2, const float* w_next, void* h,
+                            int h_dtype, long long rows, int W, float eps, void* stream);
+/* gated delta rule (csrc/delta_rule.cu): short convolution + silu + unit norm, convolution state, recurrence */
+int nxd_delta_prep(int dtype, const void* proj, long long ld, int off_q, int off_k, int off_v, const float* conv_w,
+                   const float* conv_state, float* qn, float* kn, float* vn, const int* q_start, const int* n_new,
+                   const int* seq_ids, int B, int Tn, int H, int G, int D, int Dv, int taps, float qscale, float unit_eps,
+                   void* stream);
+int nxd_delta_conv_state(int dtype, const void* proj, long long ld, int off_q, int off_k, int off_v, float* conv_state,
+                         const int* q_start, const int* n_new, const int* seq_ids, int B, int Tn, int H, int G, int D,
+                         int Dv, int taps, void* stream);
+int nxd_delta_scan(const float* qn, const float* kn, const float* vn, const float* apre, long long ld_a, int a_off,
+                   const float* bpre, long long ld_b, int b_off, const float* a_log, const float* dt_bias, float* S,
+                   float* out, const int* q_start, const int* n_new, const int* seq_ids, int B, int Tn, int H, int G, int D,
+                   int Dv, int per_channel, void* stream);
+/* gate and up columns of a wider row (+ fp32 biases or NULL) -> gated activation as in nxd_clamped_glu, out [rows, F] */
+int nxd_glu_bias(int dtype, const void* src, long long ld, int gate_off, int up_off, const float* gate_bias,
+                 const float* up_bias, void* out, long long rows, int F, float limit, float alpha, float up_shift,
+                 void* stream);
+/* router: s = softmax(wr h + zbias); the `top` largest (s + corr) are chosen, weight = s * out_scale; sgate =
+ * sigmoid(<wsg, h>).  renorm != 0: the `top` largest logits are chosen, weight = softmax over the chosen logits */
 int nxd_moe_router(int dtype, const void* h, const float* wr, const float* corr, const float* wsg, int* idx, float* wts,
-                   float* sgate, long long N, int W, int R, int top, float out_scale, void* stream);
+                   float* sgate, long long N, int W, int R, int top, float out_scale, const float* zbias, int renorm,
+                   void* stream);
 /* expert weights [E, in, out]; an index outside [0, E) is an identity expert */
 int nxd_moe_gate_up_act(int dtype, const void* h, const void* wgu, const int* idx, void* act, long long P,
-                        int pairs_per_token, int W, int F, int E, float limit, float alpha, void* stream);
+                        int pairs_per_token, int W, int F, int E, float limit, float alpha, float up_shift, void* stream);
 int nxd_moe_down_combine(int dtype, const void* act, const void* wd, const int* idx, const float* wts, const void* h,
                          const void* act_s, const void* wds, const float* sgate, float* y, long long N, int top, int W,
                          int F, int Fs, int E, void* stream);
-int nxd_clamped_glu(int dtype, const void* gate_up, void* out, long long M, int F, float limit, float alpha, void* stream);
+int nxd_clamped_glu(int dtype, const void* gate_up, void* out, long long M, int F, float limit, float alpha,
+                    float up_shift, void* stream);
 int nxd_moe_gather_combine(int dtype, const void* ys, const int* slot, const int* idx, const float* wts, const void* h,
                            const void* shared_out, const float* sgate, float* y, long long N, int top, int W, int E,
                            void* stream);

@@ -5,7 +5,7 @@ from .config import InferenceConfig  # noqa: F401
 from .kv_cache import KVCache  # noqa: F401
 from .model import (DbrxInferenceModel, GekazenInferenceModel, KVCacheInferenceMixin, LlamaInferenceModel,  # noqa: F401
                     MixtralInferenceModel)
-from .hybrid import RasodraInferenceModel  # noqa: F401
+from .hybrid import GogalixInferenceModel, RasodraInferenceModel  # noqa: F401
 from .gqa import GQA, determine_sharding_strategy, get_shardable_head_counts  # noqa: F401
 from .autobucketing import generate_buckets  # noqa: F401
 from .checkpoint import load_state_dict, save_state_dict_safetensors  # noqa: F401

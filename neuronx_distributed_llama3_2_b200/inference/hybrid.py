@@ -1,4 +1,7 @@
-"""Rasodra over the framework's step function: chunked attention, latent attention and the recurrent matrix memory on
+"""Hybrid families (recurrent mixers next to attention over the cache) over the framework's step function: Rasodra and,
+further down, Gogalix.
+
+Rasodra over the framework's step function: chunked attention, latent attention and the recurrent matrix memory on
 one KV cache / state manager.
 
 The step function (``forward_infer``: padding, cache lines through ``seq_ids``, indexed logits, sampler, ``generate``),
@@ -25,11 +28,15 @@ from typing import Dict, Optional, Tuple
 
 import torch
 
+from ..models.gogalix import UNIT_NORM_EPS, GogalixConfig, GogalixForCausalLM
 from ..models.rasodra import RasodraConfig, RasodraForCausalLM
 from ..ops import activation as act_ops
 from ..ops import attention as attn_ops
+from ..ops import delta_rule as delta_ops
 from ..ops import latent_attention as la_ops
 from ..ops import mlstm as mlstm_ops
+from ..ops import moe_sparse as moe_ops
+from ..ops import norm as norm_ops
 from ..ops import rope as rope_ops
 from ..ops import window_attention as wa_ops
 from ..ops.linear import gemm_nt
@@ -238,6 +245,158 @@ class RasodraInferenceModel(KVCacheInferenceMixin, RasodraForCausalLM):
         if self.layer_probe is not None:
             self.layer_probe(i, x)
         return x, h
+
+    def forward_speculation(self, *a, **kw):
+        raise NotImplementedError("the speculation verify graph is not wired for this family")
+
+
+class GogalixInferenceModel(KVCacheInferenceMixin, GogalixForCausalLM):
+    """Gogalix over the KV cache / state manager.  The step function (padding, cache lines through ``seq_ids``, indexed
+    logits, sampler, ``generate``), the schedulers and the runners are the mixin's; this class says what a layer does:
+
+      * ``hidden`` is the fp32 stream ``x``, ``residual`` carries ``norm1(x)`` of the layer about to run in the
+        activation dtype (the residual update of a layer and the next layer's norm are one kernel);
+      * ONE matrix product of the normed input gives the mixer's projections, its output gate, both residual gates and
+        the dense gate / up (``layer.in_proj``, parts at ``layer.columns``); the kernels read their part in place;
+      * ``attention``: the two maps of every head are separate heads of the windowed attention over the cache (queries
+        and keys map-major, the value heads shared by the two maps), then ``a1 - lambda a2`` + head norm;
+      * ``delta`` / ``channel_delta``: short convolution + silu + unit norm from the line's convolution state, the
+        gated-delta recurrence on the line's fp32 state, head norm * weight * output gate;
+      * ``x += ls1 * sigmoid(rg1) * mixer + ls2 * sigmoid(rg2) * ff`` and the next norm in one pass.
+    A step may start at any position: attention reads earlier keys from the cache, the recurrence continues from the
+    line's state."""
+
+    supports_prefill_at_offset = True
+
+    def __init__(self, config: GogalixConfig, inference_config: Optional[InferenceConfig] = None, device=None):
+        GogalixForCausalLM.__init__(self, config, device=device)
+        self._init_inference(inference_config)
+        self.layer_probe = None            # callable(i, x) after every layer run (debugging / layer-by-layer checks)
+
+    def _decoder_layers(self):
+        return self.layers
+
+    def _embedding(self):
+        return self.embed_tokens
+
+    def _final_norm(self):
+        return self.norm
+
+    def init_kv_cache(self, device=None, dtype=None) -> KVCache:
+        ic, cfg = self.inference_config, self.config
+        device = device or next(self.parameters()).device
+        specs, states, share = [], {}, {}
+        for i, L in enumerate(cfg.layers):
+            m = L.mixer
+            if L.type == "attention":
+                # the two maps' keys are 2 * kv_heads key heads (map-major); both maps read the same kv_heads value heads
+                specs.append((2 * m.kv_heads, m.dim, m.vdim, "heads", m.kv_heads))
+                if m.kv_from is not None:
+                    share[i] = m.kv_from
+            else:
+                specs.append(None)
+                states[i] = {"S": (m.heads, m.dim, m.vdim), "conv": (m.conv - 1, m.channels)}
+        self.kv_cache = KVCache(len(cfg.layers), ic.max_batch_size, 0, ic.seq_len, 0, dtype=dtype or cfg.torch_dtype,
+                                device=device, paged=ic.paged_kv, page_size=ic.page_size,
+                                num_pages=ic.num_kv_pages if ic.paged_kv else None, layer_specs=specs, share_from=share,
+                                state_specs=states)
+        return self.kv_cache
+
+    def _embed(self, input_ids: torch.Tensor) -> torch.Tensor:
+        return super()._embed(input_ids).float().mul_(self.config.embedding_scale)       # the stream is fp32
+
+    def _add_norm(self, norm, hidden: torch.Tensor, residual: Optional[torch.Tensor]):
+        """Only the model's final norm comes through here: plain one-weight RMS norm of the fp32 stream."""
+        W = hidden.shape[-1]
+        h = norm_ops.gated_residual_norm_(hidden.reshape(-1, W), None, w_next=norm, eps=self.config.rms_norm_eps,
+                                          out_dtype=self.config.torch_dtype)[1]
+        return h.reshape(hidden.shape), None
+
+    def _paged(self) -> dict:
+        kc = self.kv_cache
+        return dict(block_table=kc.block_table, page_size=kc.page_size) if kc.paged else {}
+
+    # -- mixers: big [N, n_out] = the fused projection of the normed input -> [N, W] in the activation dtype -------------
+    def _mix_attention(self, i, layer, h2, big, B, T, q_start, n_new, seq_ids):
+        mixer, m, cfg = layer.mixer, layer.mixer.cfg, self.config
+        H, G, D, Dv = m.heads, m.kv_heads, m.dim, m.vdim
+        kc = self.kv_cache
+        ck, cv = kc.layer(i)
+        owns = kc.owns(i)
+        paged = self._paged()
+        at, n = layer.columns["qkv"]
+        qkv = big.view(B, T, -1)[..., at: at + n]
+        q = wa_ops.qk_norm_cache_write(qkv, ck if owns else None, cv if owns else None, q_start, 2 * H, 2 * G, D, Dv,
+                                       cfg.rms_norm_eps, n_new=n_new, seq_ids=seq_ids, normalize=False, value_heads=G,
+                                       **paged)
+        if T == 1:
+            maps = wa_ops.window_attention_decode(q[:, 0], ck, cv, q_start, m.scale, m.window, seq_ids=seq_ids,
+                                                  value_heads=G, **paged)
+        else:
+            maps = wa_ops.window_attention_prefill(q, ck, cv, q_start, m.scale, m.window, n_new=n_new, seq_ids=seq_ids,
+                                                   value_heads=G, **paged)
+        o = wa_ops.diff_attention_combine(maps.reshape(B * T, 2 * H, Dv), mixer.lq1, mixer.lk1, mixer.lq2, mixer.lk2,
+                                          m.diff, cfg.rms_norm_eps)
+        return gemm_nt(o, mixer.o_proj.weight)
+
+    def _mix_delta(self, i, layer, h2, big, B, T, q_start, n_new, seq_ids):
+        mixer, m, cfg, dt = layer.mixer, layer.mixer.cfg, self.config, self.config.torch_dtype
+        H, G, D, Dv, N = m.heads, m.kv_heads, m.dim, m.vdim, B * T
+        st = self.kv_cache.state(i)
+        at = layer.columns["qkv"][0]
+        qn, kn, vn = delta_ops.delta_prep(big.view(B, T, -1), (at, at + G * D, at + 2 * G * D), mixer.conv_weight,
+                                          st["conv"], q_start, H, G, D, Dv, D ** -0.5, UNIT_NORM_EPS, n_new=n_new,
+                                          seq_ids=seq_ids)
+        # pre-activations of the recurrence's gates stay fp32: beta rows, then (one decay per head) the decay rows
+        gates = gemm_nt(h2, mixer.gate_proj, out_dtype=torch.float32)
+        if m.per_channel:
+            rk = mixer.a2.shape[1]              # the low-rank inner size, padded; the padding columns of `big` are zeros
+            a_pre = gemm_nt(big[:, layer.columns["a1"][0]:][:, :rk].contiguous(), mixer.a2, out_dtype=torch.float32)
+            a_off = 0
+            gate_src = gemm_nt(big[:, layer.columns["g1"][0]:][:, :rk].contiguous(), mixer.g2)
+            gate_off, gate_act = 0, "sigmoid"
+        else:
+            a_pre, a_off = gates, H
+            gate_src, gate_off, gate_act = big, layer.columns["g"][0], "silu"
+        o = delta_ops.delta_scan(qn, kn, vn, a_pre, a_off, gates, 0, mixer.a_log, mixer.dt_bias, st["S"], q_start,
+                                 m.per_channel, n_new=n_new, seq_ids=seq_ids)
+        y = mlstm_ops.head_norm_gate(o.reshape(N, H, Dv), gate_src, gate_off, H, Dv, mixer.out_norm, cfg.rms_norm_eps,
+                                     True, dt, gate_act=gate_act)
+        return gemm_nt(y, mixer.o_proj.weight)
+
+    _MIX = {"attention": _mix_attention, "delta": _mix_delta, "channel_delta": _mix_delta}
+
+    # -- one layer --------------------------------------------------------------------------------------------------
+    def _layer(self, i: int, layer, hidden, residual, positions, seq_ids, lengths, prefill):
+        cfg, dt = self.config, self.config.torch_dtype
+        B, T, W = hidden.shape
+        N = B * T
+        x = (hidden if hidden.is_contiguous() else hidden.contiguous()).view(N, W)
+        h2 = (residual.reshape(N, W) if residual is not None else
+              norm_ops.gated_residual_norm_(x, None, w_next=layer.norm1, eps=cfg.rms_norm_eps, out_dtype=dt)[1])
+        if "q_start" not in self._step_kv:      # one int32 copy of the rows' first positions per step, not per kernel
+            self._step_kv["q_start"] = positions[:, 0].to(torch.int32).contiguous()
+        q_start = self._step_kv["q_start"]
+        n_new = self._step_new_tokens if prefill else None
+        big = gemm_nt(h2, layer.in_proj.weight)
+        cols = layer.columns
+        y1 = self._MIX[layer.type](self, i, layer, h2, big, B, T, q_start, n_new, seq_ids)
+        y2 = y2_bias = None
+        if layer.mlp_kind == "dense":
+            ff = layer.mlp.gate_bias.shape[0]
+            act = moe_ops.glu_bias(big, cols["gate"][0], cols["up"][0], ff, layer.mlp.gate_bias, layer.mlp.up_bias)
+            y2, y2_bias = gemm_nt(act, layer.mlp.down_proj.weight), layer.mlp.down_bias
+        elif layer.mlp_kind == "moe":
+            y2 = layer.mlp(h2)                                       # fp32 [N, W]
+        nxt = self.layers[i + 1].norm1 if i + 1 < len(self.layers) else None
+        has_ff = layer.mlp_kind is not None
+        x, h_next = norm_ops.gated_residual_norm_(
+            x, y1, y2, y2_bias, gate=big, gate_offsets=(cols["rg1"][0], cols["rg2"][0] if has_ff else 0),
+            gate_bias1=layer.rg1_bias, gate_bias2=layer.rg2_bias if has_ff else None, scale1=layer.ls1,
+            scale2=layer.ls2 if has_ff else None, w_next=nxt, eps=cfg.rms_norm_eps, out_dtype=dt)
+        if self.layer_probe is not None:
+            self.layer_probe(i, x.view(B, T, W))
+        return x.view(B, T, W), (h_next.view(B, T, W) if h_next is not None else None)
 
     def forward_speculation(self, *a, **kw):
         raise NotImplementedError("the speculation verify graph is not wired for this family")

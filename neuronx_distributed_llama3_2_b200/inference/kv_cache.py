@@ -16,7 +16,8 @@ value sizes may differ), and ``share_from[i] = j`` makes layer ``i`` read layer 
 holding its own (cross-layer KV sharing: ``layer(i)`` returns ``j``'s tensors, nothing is allocated for ``i``).
 A spec ``(kv_heads, key_dim, value_dim, "columns")`` keeps ONE tensor per layer whose value is the first ``value_dim``
 columns of the key rows (the latent cache of a compressed key/value projection); a spec ``None`` is a layer without
-keys and values.
+keys and values; a spec ``(kv_heads, key_dim, value_dim, "heads", value_heads)`` gives the value tensor its own number
+of heads (several attention maps -- key heads -- over the same values).
 
 Recurrent layers keep a STATE per cache line instead: ``state_specs[i] = {name: shape}`` allocates fp32 tensors
 ``[lines, *shape]`` (``state(i)``).  State is per line, not per page: ``fork`` copies it, and a layer that starts a
@@ -74,6 +75,8 @@ class KVCache:
             self.k.append(torch.zeros((lead, g, rows, dk), dtype=dtype, device=device))
             if len(specs[i]) > 3 and specs[i][3] == "columns":
                 self.v.append(self.k[-1][..., :dv])    # the values are columns of the key rows: one tensor
+            elif len(specs[i]) > 4 and specs[i][3] == "heads":
+                self.v.append(torch.zeros((lead, int(specs[i][4]), rows, dv), dtype=dtype, device=device))
             else:
                 self.v.append(torch.zeros((lead, g, rows, dv), dtype=dtype, device=device))
         self.states: Dict[int, Dict[str, torch.Tensor]] = {

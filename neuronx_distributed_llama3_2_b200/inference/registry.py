@@ -106,11 +106,31 @@ def _rasodra_cls():
     return RasodraInferenceModel
 
 
+def _gogalix_config(d, dtype):
+    from ..models.gogalix import GogalixConfig
+
+    return GogalixConfig.from_dict(d, torch_dtype=dtype)
+
+
+def _gogalix_convert(sd, cfg):
+    from ..models.gogalix import convert_gogalix_state_dict
+
+    return convert_gogalix_state_dict(sd, cfg)
+
+
+def _gogalix_cls():
+    from .hybrid import GogalixInferenceModel
+
+    return GogalixInferenceModel
+
+
 register_family(ModelFamily("llama", lambda c: _arch(c).startswith("llama"), _llama_config, _llama_cls, _llama_convert))
 register_family(ModelFamily("gekazen", lambda c: _arch(c) == "gekazen", _gekazen_config, _gekazen_cls, _gekazen_convert,
                             kernel_group="window_moe_serving"))
 register_family(ModelFamily("rasodra", lambda c: _arch(c) == "rasodra", _rasodra_config, _rasodra_cls, _rasodra_convert,
                             kernel_group="hybrid_serving"))
+register_family(ModelFamily("gogalix", lambda c: _arch(c) == "gogalix", _gogalix_config, _gogalix_cls, _gogalix_convert,
+                            kernel_group="delta_serving"))
 
 
 def read_config(model_dir: str) -> Dict[str, Any]:
@@ -132,9 +152,12 @@ def load_model(model_dir: str, dtype: torch.dtype = torch.bfloat16, inference_co
     cfg = fam.make_config(raw, dtype)
     device = device or (torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available()
                         else torch.device("cpu"))
+    raw_sd = load_state_dict(model_dir) if load_weights else None
+    if raw_sd is not None and hasattr(cfg, "with_checkpoint_shapes"):
+        cfg.with_checkpoint_shapes(raw_sd)         # sizes that only the tensors' shapes tell (a low-rank inner size)
     model = fam.model_cls()(cfg, inference_config, device=device)
     if load_weights:
-        sd = fam.convert_state_dict(load_state_dict(model_dir), cfg)
+        sd = fam.convert_state_dict(raw_sd, cfg)
         missing, unexpected = model.load_state_dict(sd, strict=False)
         missing = [k for k in missing if not k.endswith("slopes")]
         if missing or unexpected:

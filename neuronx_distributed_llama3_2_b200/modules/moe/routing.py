@@ -109,14 +109,20 @@ class RouterBiasedTopK(RouterBase):
     weights are the chosen experts' plain scores times ``affinity_scale``, not renormalised.  The last
     ``num_identity_experts`` outputs are identity experts (their output is their input; they have no weights).  The
     router runs in fp32 whatever the activation dtype; ``select`` is the fused device path (one kernel: projection,
-    softmax, choice, optional sigmoid gate of a shared expert)."""
+    softmax, choice, optional sigmoid gate of a shared expert).  ``bias``: a bias on the logits (``logit_bias``);
+    ``renormalize``: the experts with the largest logits are chosen and their weights are the softmax over the chosen
+    logits only."""
 
     def __init__(self, num_experts: int, top_k: int, hidden_size: int, num_identity_experts: int = 0,
-                 affinity_scale: float = 1.0, device: torch.device = torch.device("cpu")):
+                 affinity_scale: float = 1.0, device: torch.device = torch.device("cpu"), bias: bool = False,
+                 renormalize: bool = False):
         super().__init__(num_experts + num_identity_experts, top_k, hidden_size, "softmax", torch.float32, device)
         self.num_real_experts = num_experts
         self.num_identity_experts = num_identity_experts
         self.affinity_scale = affinity_scale
+        self.renormalize = renormalize
+        self.logit_bias = torch.nn.Parameter(torch.zeros(num_experts + num_identity_experts, dtype=torch.float32,
+                                                         device=device), requires_grad=False) if bias else None
         self.correction = torch.nn.Parameter(torch.zeros(num_experts + num_identity_experts, dtype=torch.float32,
                                                          device=device), requires_grad=False)
 
@@ -126,11 +132,17 @@ class RouterBiasedTopK(RouterBase):
 
         flat = hidden_states.reshape(-1, hidden_states.shape[-1])
         return moe_sparse.route(flat, self.linear_router.weight, self.correction, self.top_k, self.affinity_scale,
-                                shared_gate_weight)
+                                shared_gate_weight, self.logit_bias, self.renormalize)
 
     def forward(self, hidden_states):
         flat = hidden_states.reshape(-1, hidden_states.shape[-1])
         router_logits = flat.float() @ self.linear_router.weight.float().t()
+        if self.logit_bias is not None:
+            router_logits = router_logits + self.logit_bias.float()
+        if self.renormalize:     # affinities: softmax over the chosen logits, zero elsewhere
+            val, expert_index = torch.topk(router_logits, self.top_k, dim=1)
+            scores = torch.zeros_like(router_logits).scatter(1, expert_index, torch.softmax(val, dim=1))
+            return router_logits, scores * self.affinity_scale, expert_index.detach().to(torch.long)
         scores = self.apply_activation_fn(router_logits)
         _, expert_index = torch.topk(scores + self.correction.float(), self.top_k, dim=1)
         return router_logits, scores * self.affinity_scale, expert_index.detach().to(torch.long)

@@ -1,5 +1,7 @@
 """``SparseMoE``: dropless inference feed-forward built from the MoE pieces of this package -- a ``RouterBiasedTopK``,
-the grouped ``Experts`` (clamped gated activation), optional identity experts and an optional gated shared expert.
+the grouped ``Experts`` (clamped gated activation, or the plain ``silu(gate) * up`` with ``limit=None``), optional
+identity experts and an optional gated shared expert.  ``router_bias``: the router has a bias on its logits;
+``renormalize``: the experts with the largest logits are chosen and weighted by the softmax over the chosen logits only.
 
 Two execution paths over the same parameters:
   * pairs   every (token, choice) pair runs a GEMV against the chosen expert's weights, picked by the index ON THE
@@ -29,20 +31,26 @@ class SparseMoE(torch.nn.Module):
     def __init__(self, hidden_size: int, num_experts: int, top_k: int, intermediate_size: int, limit: float,
                  num_identity_experts: int = 0, affinity_scale: float = 1.0, shared_intermediate_size: int = 0,
                  shared_limit: Optional[float] = None, alpha: float = moe_sparse.GLU_ALPHA,
-                 dtype: torch.dtype = torch.float32, device=None):
+                 dtype: torch.dtype = torch.float32, device=None, router_bias: bool = False, renormalize: bool = False):
         super().__init__()
         dev = device if device is not None else torch.device("cpu")
         self.hidden_size, self.num_experts, self.top_k = hidden_size, num_experts, top_k
+        if limit is None:            # plain silu(gate) * up: no clamp, unit slope, no shift of the linear half
+            limit, alpha, self.up_shift = float("inf"), 1.0, 0.0
+        else:
+            self.up_shift = 1.0
+        shift = self.up_shift
         self.limit, self.alpha = limit, alpha
-        self.router = RouterBiasedTopK(num_experts, top_k, hidden_size, num_identity_experts, affinity_scale, device=dev)
+        self.router = RouterBiasedTopK(num_experts, top_k, hidden_size, num_identity_experts, affinity_scale, device=dev,
+                                       bias=router_bias, renormalize=renormalize)
         self.experts = Experts(num_experts, hidden_size, intermediate_size, True, None, dtype=dtype, device=dev,
-                               glu_fn=lambda gu: moe_sparse.clamped_glu(gu, limit, alpha))
+                               glu_fn=lambda gu: moe_sparse.clamped_glu(gu, limit, alpha, shift))
         self.shared = None
         if shared_intermediate_size > 0:
             sl = shared_limit if shared_limit is not None else limit
             self.shared_limit = sl
             self.shared = Experts(1, hidden_size, shared_intermediate_size, True, None, dtype=dtype, device=dev,
-                                  glu_fn=lambda gu: moe_sparse.clamped_glu(gu, sl, alpha))
+                                  glu_fn=lambda gu: moe_sparse.clamped_glu(gu, sl, alpha, shift))
             self.shared_gate = LinearRouter(hidden_size, 1, dtype=torch.float32, device=dev)
 
     def _use_sorted(self, n_tokens: int) -> bool:
@@ -58,10 +66,11 @@ class SparseMoE(torch.nn.Module):
         if sorted_path:
             return self._forward_sorted(h, idx, wts, sg)
         w_gu, w_d = self.experts.gate_up_proj.weight, self.experts.down_proj.weight
-        act = moe_sparse.gate_up_act(h, w_gu, idx, self.limit, self.alpha)
+        act = moe_sparse.gate_up_act(h, w_gu, idx, self.limit, self.alpha, self.up_shift)
         s_act = s_down = None
         if self.shared is not None:
-            s_act = moe_sparse.gate_up_act(h, self.shared.gate_up_proj.weight, None, self.shared_limit, self.alpha)
+            s_act = moe_sparse.gate_up_act(h, self.shared.gate_up_proj.weight, None, self.shared_limit, self.alpha,
+                                           self.up_shift)
             s_down = self.shared.down_proj.weight[0]
         return moe_sparse.down_combine(act, w_d, idx, wts, h, s_act, s_down, sg)
 

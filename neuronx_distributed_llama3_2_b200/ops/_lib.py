@@ -55,8 +55,14 @@ GROUPS["hybrid_serving"] = ["window_attention.cu", "post_norm.cu", "latent_atten
                             "gemm_tcgen05.cu", "gemm_smallm.cu", "fused_gemm_ar.cu", "tma_host.cu", "flash_attn_tc.cu",
                             "attn_tc_host.cu"]
 
+# the delta-rule hybrids (gated delta rule, differential window attention, dense and sparse gated feed-forward on a
+# gated parallel residual): the attention-over-cache, norm, sparse-MoE and recurrent-output kernels, the recurrence's
+# own source and the GEMM kernels behind the linear layers
+GROUPS["delta_serving"] = ["window_attention.cu", "post_norm.cu", "moe_sparse.cu", "mlstm.cu", "delta_rule.cu",
+                           "runtime.cu", "gemm_tcgen05.cu", "gemm_smallm.cu", "fused_gemm_ar.cu", "tma_host.cu"]
+
 # sources whose fp32 state is carried over thousands of steps: no approximate exp / tanh / division
-PRECISE_SOURCES = {"mlstm.cu"}
+PRECISE_SOURCES = {"mlstm.cu", "delta_rule.cu"}
 
 _lib: Optional[ctypes.CDLL] = None
 _group_libs = {}

@@ -227,21 +227,24 @@ def mlstm_chunkwise(proj: torch.Tensor, offsets: Tuple[int, int, int], gi: torch
 
 
 def head_norm_gate(o: torch.Tensor, gate_src: torch.Tensor, gate_offset: int, heads: int, vdim: int,
-                   weight: Optional[torch.Tensor], eps: float, normalize: bool, out_dtype: torch.dtype) -> torch.Tensor:
+                   weight: Optional[torch.Tensor], eps: float, normalize: bool, out_dtype: torch.dtype,
+                   gate_act: str = "sigmoid") -> torch.Tensor:
     """``o [N, heads, vdim]`` -> ``[N, heads * vdim]`` in ``out_dtype``: every head divided by its root mean square
     (``normalize``; fp32, ``eps`` inside the root), times ``weight [heads * vdim]`` (optional), times
-    ``sigmoid(gate)`` where the gate pre-activations are columns ``gate_offset ...`` of ``gate_src [N, ld]``."""
+    ``sigmoid(gate)`` (or ``silu(gate)`` with ``gate_act="silu"``) where the gate pre-activations are columns
+    ``gate_offset ...`` of ``gate_src [N, ld]`` (rows ``gate_src.stride(0)`` apart)."""
     N = o.shape[0]
-    ld = gate_src.shape[-1]
-    if (_use_kernel(gate_src) and gate_src.dtype == out_dtype and gate_src.is_contiguous() and o.is_contiguous()
-            and (o.dtype == torch.float32 or o.dtype == out_dtype)):
+    gate_src = gate_src.reshape(N, -1) if gate_src.is_contiguous() else gate_src
+    ld = gate_src.stride(0) if gate_src.dim() == 2 else gate_src.shape[-1]
+    if (_use_kernel(gate_src) and gate_src.dtype == out_dtype and gate_src.dim() == 2 and gate_src.stride(1) == 1
+            and o.is_contiguous() and (o.dtype == torch.float32 or o.dtype == out_dtype)):
         out = torch.empty(N, heads * vdim, dtype=out_dtype, device=o.device)
         wf = weight.float().contiguous() if weight is not None else None
         L = _lib.lib(GROUP)
         rc = L.nxd_head_norm_gate(_c.c_int(_code(o.dtype)), _c.c_int(_code(out_dtype)), _lib.ptr(o), _lib.ptr(gate_src),
                                   _c.c_longlong(ld), _c.c_int(gate_offset), _lib.ptr(wf), _lib.ptr(out), _c.c_longlong(N),
                                   _c.c_int(heads), _c.c_int(vdim), _c.c_int(int(normalize)), _c.c_float(eps),
-                                  _lib.stream_ptr())
+                                  _c.c_int(1 if gate_act == "silu" else 0), _lib.stream_ptr())
         _lib.check(rc, "nxd_head_norm_gate", L)
         return out
     of = o.float().reshape(N, heads, vdim)
@@ -250,5 +253,5 @@ def head_norm_gate(o: torch.Tensor, gate_src: torch.Tensor, gate_offset: int, he
     of = of.reshape(N, heads * vdim)
     if weight is not None:
         of = of * weight.float()
-    g = gate_src.reshape(N, ld)[:, gate_offset: gate_offset + heads * vdim].float()
-    return (of * torch.sigmoid(g)).to(out_dtype)
+    g = gate_src.reshape(N, -1)[:, gate_offset: gate_offset + heads * vdim].float()
+    return (of * (F.silu(g) if gate_act == "silu" else torch.sigmoid(g))).to(out_dtype)

@@ -2,8 +2,10 @@
 additive correction that only steers the CHOICE, un-renormalised scaled weights and identity experts; expert GEMVs that
 follow the expert index without a host round trip; a clamped gated activation; the weighted combination in fp32.
 
-    s = softmax(Wr h);  chosen = top-k of (s + correction);  weight = s[chosen] * scale
-    act(g, u) = g' * sigmoid(alpha * g') * (u' + 1),  g' = min(g, limit),  u' = clamp(u, -limit, limit)
+    s = softmax(Wr h + b);  chosen = top-k of (s + correction);  weight = s[chosen] * scale
+    renormalised form:  chosen = top-k of the logits,  weight = softmax over the chosen logits only
+    act(g, u) = g' * sigmoid(alpha * g') * (u' + shift),  g' = min(g, limit),  u' = clamp(u, -limit, limit)
+    (limit = inf, alpha = 1, shift = 0 is the plain silu(g) * u)
     expert index >= E: identity expert (output = input)
 
 Expert weights use the layout of the grouped expert layers (``modules/moe``): ``gate_up [E, W, 2F]``, ``down [E, F, W]``.
@@ -30,13 +32,14 @@ def _use_kernel(x: torch.Tensor) -> bool:
     return x.is_cuda and x.dtype in (torch.bfloat16, torch.float32) and _lib.available(GROUP)
 
 
-def clamped_glu_ref(gate: torch.Tensor, up: torch.Tensor, limit: float, alpha: float = GLU_ALPHA) -> torch.Tensor:
+def clamped_glu_ref(gate: torch.Tensor, up: torch.Tensor, limit: float, alpha: float = GLU_ALPHA,
+                    up_shift: float = 1.0) -> torch.Tensor:
     g = gate.float().clamp(max=limit)
     u = up.float().clamp(-limit, limit)
-    return (g * torch.sigmoid(alpha * g) * (u + 1.0)).to(gate.dtype)
+    return (g * torch.sigmoid(alpha * g) * (u + up_shift)).to(gate.dtype)
 
 
-def clamped_glu(gate_up: torch.Tensor, limit: float, alpha: float = GLU_ALPHA) -> torch.Tensor:
+def clamped_glu(gate_up: torch.Tensor, limit: float, alpha: float = GLU_ALPHA, up_shift: float = 1.0) -> torch.Tensor:
     """``gate_up [..., 2F]`` (gate | up) -> ``[..., F]``."""
     F = gate_up.shape[-1] // 2
     if _use_kernel(gate_up):
@@ -44,15 +47,45 @@ def clamped_glu(gate_up: torch.Tensor, limit: float, alpha: float = GLU_ALPHA) -
         out = torch.empty(gu.shape[:-1] + (F,), dtype=gu.dtype, device=gu.device)
         L = _lib.lib(GROUP)
         rc = L.nxd_clamped_glu(_c.c_int(_code(gu.dtype)), _lib.ptr(gu), _lib.ptr(out), _c.c_longlong(gu.numel() // (2 * F)),
-                               _c.c_int(F), _c.c_float(limit), _c.c_float(alpha), _lib.stream_ptr())
+                               _c.c_int(F), _c.c_float(limit), _c.c_float(alpha), _c.c_float(up_shift), _lib.stream_ptr())
         _lib.check(rc, "nxd_clamped_glu", L)
         return out
-    return clamped_glu_ref(gate_up[..., :F], gate_up[..., F:], limit, alpha)
+    return clamped_glu_ref(gate_up[..., :F], gate_up[..., F:], limit, alpha, up_shift)
+
+
+def glu_bias(src: torch.Tensor, gate_offset: int, up_offset: int, width: int, gate_bias: Optional[torch.Tensor] = None,
+             up_bias: Optional[torch.Tensor] = None, limit: Optional[float] = None, alpha: float = GLU_ALPHA,
+             up_shift: float = 1.0) -> torch.Tensor:
+    """Gated activation whose gate and up halves are column ranges of a wider projection output ``src [M, ld]``, each
+    with an optional fp32 bias -> ``[M, width]``.  ``limit=None``: the plain ``silu(gate) * up``."""
+    if limit is None:
+        limit, alpha, up_shift = float("inf"), 1.0, 0.0
+    M = src.shape[0]
+    if _use_kernel(src) and src.stride(1) == 1:
+        out = torch.empty(M, width, dtype=src.dtype, device=src.device)
+        gb = gate_bias.float().contiguous() if gate_bias is not None else None
+        ub = up_bias.float().contiguous() if up_bias is not None else None
+        L = _lib.lib(GROUP)
+        rc = L.nxd_glu_bias(_c.c_int(_code(src.dtype)), _lib.ptr(src), _c.c_longlong(src.stride(0)), _c.c_int(gate_offset),
+                            _c.c_int(up_offset), _lib.ptr(gb), _lib.ptr(ub), _lib.ptr(out), _c.c_longlong(M),
+                            _c.c_int(width), _c.c_float(limit), _c.c_float(alpha), _c.c_float(up_shift), _lib.stream_ptr())
+        _lib.check(rc, "nxd_glu_bias", L)
+        return out
+    g = src[:, gate_offset: gate_offset + width].float()
+    u = src[:, up_offset: up_offset + width].float()
+    if gate_bias is not None:
+        g = g + gate_bias.float()
+    if up_bias is not None:
+        u = u + up_bias.float()
+    return clamped_glu_ref(g, u, limit, alpha, up_shift).to(src.dtype)
 
 
 def route(h: torch.Tensor, router_w: torch.Tensor, correction: Optional[torch.Tensor], top: int, scale: float,
-          shared_gate_w: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
-    """``h [N, W]``, ``router_w [R, W]`` fp32 -> ``(index [N, top] int32, weight [N, top] fp32, shared gate [N] fp32)``."""
+          shared_gate_w: Optional[torch.Tensor] = None, logit_bias: Optional[torch.Tensor] = None,
+          renormalize: bool = False) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
+    """``h [N, W]``, ``router_w [R, W]`` fp32 -> ``(index [N, top] int32, weight [N, top] fp32, shared gate [N] fp32)``.
+    ``logit_bias [R]`` is added to the logits; ``renormalize``: the largest logits are chosen and weighted by the softmax
+    over the chosen logits only (``correction`` does not apply)."""
     N, W = h.shape
     R = router_w.shape[0]
     if _use_kernel(h) and router_w.dtype == torch.float32:
@@ -62,23 +95,31 @@ def route(h: torch.Tensor, router_w: torch.Tensor, correction: Optional[torch.Te
         sg = torch.empty(N, dtype=torch.float32, device=h.device) if shared_gate_w is not None else None
         corr = correction.float().contiguous() if correction is not None else None
         wsg = shared_gate_w.float().reshape(-1).contiguous() if shared_gate_w is not None else None
+        zb = logit_bias.float().contiguous() if logit_bias is not None else None
         L = _lib.lib(GROUP)
         rc = L.nxd_moe_router(_c.c_int(_code(h.dtype)), _lib.ptr(h), _lib.ptr(router_w.contiguous()), _lib.ptr(corr),
                               _lib.ptr(wsg), _lib.ptr(idx), _lib.ptr(wts), _lib.ptr(sg), _c.c_longlong(N), _c.c_int(W),
-                              _c.c_int(R), _c.c_int(top), _c.c_float(scale), _lib.stream_ptr())
+                              _c.c_int(R), _c.c_int(top), _c.c_float(scale), _lib.ptr(zb), _c.c_int(int(renormalize)),
+                              _lib.stream_ptr())
         _lib.check(rc, "nxd_moe_router", L)
         return idx, wts, sg
     hf = h.float()
-    s = torch.softmax(hf @ router_w.float().t(), dim=-1)
+    z = hf @ router_w.float().t()
+    if logit_bias is not None:
+        z = z + logit_bias.float()
+    sg = torch.sigmoid(hf @ shared_gate_w.float().reshape(-1)) if shared_gate_w is not None else None
+    if renormalize:
+        val, idx = torch.topk(z, top, dim=-1)
+        return idx.to(torch.int32), torch.softmax(val, dim=-1) * scale, sg
+    s = torch.softmax(z, dim=-1)
     choice = s + correction.float() if correction is not None else s
     idx = torch.topk(choice, top, dim=-1).indices
     wts = s.gather(1, idx) * scale
-    sg = torch.sigmoid(hf @ shared_gate_w.float().reshape(-1)) if shared_gate_w is not None else None
     return idx.to(torch.int32), wts, sg
 
 
 def gate_up_act(h: torch.Tensor, w_gate_up: torch.Tensor, idx: Optional[torch.Tensor], limit: float,
-                alpha: float = GLU_ALPHA) -> torch.Tensor:
+                alpha: float = GLU_ALPHA, up_shift: float = 1.0) -> torch.Tensor:
     """Activated intermediate of every (token, choice) pair: ``h [N, W]``, ``w_gate_up [E, W, 2F]``, ``idx [N, top]`` (or
     ``None``: one dense expert, ``top = 1``) -> ``[N * top, F]``.  Rows of identity experts are left untouched (zeros)."""
     N, W = h.shape
@@ -91,7 +132,8 @@ def gate_up_act(h: torch.Tensor, w_gate_up: torch.Tensor, idx: Optional[torch.Te
         L = _lib.lib(GROUP)
         rc = L.nxd_moe_gate_up_act(_c.c_int(_code(h.dtype)), _lib.ptr(h), _lib.ptr(w_gate_up), _lib.ptr(idx),
                                    _lib.ptr(act), _c.c_longlong(N * top), _c.c_int(top), _c.c_int(W), _c.c_int(F),
-                                   _c.c_int(E), _c.c_float(limit), _c.c_float(alpha), _lib.stream_ptr())
+                                   _c.c_int(E), _c.c_float(limit), _c.c_float(alpha), _c.c_float(up_shift),
+                                   _lib.stream_ptr())
         _lib.check(rc, "nxd_moe_gate_up_act", L)
         return act
     act = torch.zeros(N * top, F, dtype=h.dtype, device=h.device)
@@ -101,7 +143,7 @@ def gate_up_act(h: torch.Tensor, w_gate_up: torch.Tensor, idx: Optional[torch.Te
         rows = (e_of == e).nonzero().reshape(-1)
         if rows.numel():
             gu = h[tok[rows]].float() @ w_gate_up[e].float()
-            act[rows] = clamped_glu_ref(gu[:, :F], gu[:, F:], limit, alpha).to(h.dtype)
+            act[rows] = clamped_glu_ref(gu[:, :F], gu[:, F:], limit, alpha, up_shift).to(h.dtype)
     return act
 
 

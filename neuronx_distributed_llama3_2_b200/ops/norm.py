@@ -171,3 +171,61 @@ def norm_chain_(x: torch.Tensor, y: Optional[torch.Tensor], w_post: Optional[tor
     if y is not None:
         x.add_(norm_ref(y, w_post, eps, center))
     return x, (norm_ref(x, w_next, eps, center).to(out_dtype) if w_next is not None else None)
+
+
+# ---- parallel sublayers with layer scale and a gated residual, and the next norm, in one pass (``csrc/post_norm.cu``) ----
+def gated_residual_norm_(x: torch.Tensor, y1: Optional[torch.Tensor], y2: Optional[torch.Tensor] = None,
+                         y2_bias: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
+                         gate_offsets=(0, 0), gate_bias1: Optional[torch.Tensor] = None,
+                         gate_bias2: Optional[torch.Tensor] = None, scale1: Optional[torch.Tensor] = None,
+                         scale2: Optional[torch.Tensor] = None, w_next: Optional[torch.Tensor] = None, eps: float = 1e-6,
+                         out_dtype: Optional[torch.dtype] = None):
+    """On the fp32 stream ``x [rows, W]``, in place:
+
+        x += scale1 * sigmoid(gate[:, o1:o1+W] + gate_bias1) * y1 + scale2 * sigmoid(gate[:, o2:o2+W] + gate_bias2) * (y2 + y2_bias)
+
+    then ``h = (x / sqrt(mean(x^2) + eps) * w_next).to(out_dtype)`` where ``w_next`` is ONE number (an RMS norm with a
+    single weight for all coordinates).  ``y1 = None``: no update (the plain norm of the stream); ``y2``, ``gate``,
+    scales, biases and ``w_next`` are optional.  ``gate [rows, ld]`` may be a wider projection output whose columns
+    ``o1 ...`` / ``o2 ...`` are the two gates' pre-activations.  Returns ``(x, h)``."""
+    assert x.dtype == torch.float32 and x.dim() == 2
+    rows, W = x.shape
+    ok = lambda t: t is None or (t.dtype in (torch.bfloat16, torch.float32) and t.stride(-1) == 1)     # noqa: E731
+    if x.is_cuda and ok(y1) and ok(y2) and ok(gate) and _lib.available("delta_serving"):
+        assert x.is_contiguous()
+        y1c = None if y1 is None else (y1 if y1.is_contiguous() else y1.contiguous())
+        y2c = None if y2 is None else (y2 if y2.is_contiguous() else y2.contiguous())
+        f32 = lambda t: None if t is None else t.float().contiguous()                                    # noqa: E731
+        wn, b2, g1, g2, s1, s2 = f32(w_next), f32(y2_bias), f32(gate_bias1), f32(gate_bias2), f32(scale1), f32(scale2)
+        h = torch.empty(rows, W, dtype=out_dtype, device=x.device) if wn is not None else None
+        code = lambda t: 1 if (t is None or t.dtype == torch.float32) else 0                            # noqa: E731
+        L = _lib.lib("delta_serving")
+        rc = L.nxd_gated_residual_norm(_lib.ptr(x), _lib.ptr(y1c), _c.c_int(code(y1c)), _lib.ptr(y2c), _c.c_int(code(y2c)),
+                                       _lib.ptr(b2), _lib.ptr(gate), _c.c_int(code(gate)),
+                                       _c.c_longlong(gate.stride(0) if gate is not None else 0),
+                                       _c.c_int(gate_offsets[0]), _c.c_int(gate_offsets[1]), _lib.ptr(g1), _lib.ptr(g2),
+                                       _lib.ptr(s1), _lib.ptr(s2), _lib.ptr(wn), _lib.ptr(h),
+                                       _c.c_int(_post_code(out_dtype) if h is not None else 1), _c.c_longlong(rows),
+                                       _c.c_int(W), _c.c_float(eps), _lib.stream_ptr())
+        _lib.check(rc, "nxd_gated_residual_norm", L)
+        return x, h
+
+    def term(y, bias, off, gbias, scale):
+        v = y.float()
+        if bias is not None:
+            v = v + bias.float()
+        if scale is not None:
+            v = v * scale.float()
+        if gate is not None:
+            z = gate[:, off: off + W].float()
+            v = v * torch.sigmoid(z + gbias.float() if gbias is not None else z)
+        return v
+
+    if y1 is not None:
+        upd = term(y1, None, gate_offsets[0], gate_bias1, scale1)
+        if y2 is not None:
+            upd = upd + term(y2, y2_bias, gate_offsets[1], gate_bias2, scale2)
+        x.add_(upd)
+    if w_next is None:
+        return x, None
+    return x, (x / torch.sqrt(x.pow(2).mean(-1, keepdim=True) + eps) * w_next.float().reshape(())).to(out_dtype)

@@ -77,7 +77,7 @@ def qk_norm_cache_write(qkv: torch.Tensor, cache_k: Optional[torch.Tensor], cach
                         normalize: bool = True, block_table: Optional[torch.Tensor] = None,
                         page_size: int = 0, writeback: bool = False, q_weight: Optional[torch.Tensor] = None,
                         k_weight: Optional[torch.Tensor] = None, rope: Optional[tuple] = None,
-                        value_from_key: bool = False) -> torch.Tensor:
+                        value_from_key: bool = False, value_heads: Optional[int] = None) -> torch.Tensor:
     """``q_weight / k_weight [dim]``: weight of the per-head norm (after the division).  ``rope = (cos, sin)`` tables
     ``[positions, rot/2]`` (``ops.rope.build_interleaved_rope_cache``): queries and keys turn pairwise on their first
     ``rot`` dimensions, after the norm.  ``value_from_key``: the projection has no value columns, the cached value is
@@ -87,15 +87,21 @@ def qk_norm_cache_write(qkv: torch.Tensor, cache_k: Optional[torch.Tensor], cach
     key and value heads of the real rows (``t < n_new[b]``) are written at position ``q_start[b] + t`` of cache line
     ``seq_ids[b]``.  ``normalize``: queries and keys are divided by their root mean square over ``dim`` (fp32, ``eps``
     inside the root) before they are written.  ``writeback``: the normalised keys of the real rows also replace the
-    raw ones inside ``qkv`` (for a kernel that reads q / k / v as strided views of the projection output)."""
+    raw ones inside ``qkv`` (for a kernel that reads q / k / v as strided views of the projection output).
+    ``value_heads``: the row holds that many value heads instead of ``kv_heads`` (value head ``g`` then serves the key
+    heads ``g, g + value_heads, ...``: several attention maps over the same values).  ``qkv`` may be a column range of
+    a wider projection output (rows ``stride(1)`` apart)."""
     B, T, n_out = qkv.shape
     has_kv = cache_k is not None
-    n_v = 0 if value_from_key else kv_heads * vdim
+    gv = kv_heads if value_heads is None else int(value_heads)
+    n_v = 0 if value_from_key else gv * vdim
     assert n_out == heads * dim + ((kv_heads * dim + n_v) if has_kv else 0), (n_out, heads, kv_heads, dim, vdim)
-    assert not value_from_key or vdim == dim
+    assert not value_from_key or (vdim == dim and gv == kv_heads)
     if _use_kernel(qkv):
-        assert qkv.is_contiguous() or not writeback
-        qkv = qkv if qkv.is_contiguous() else qkv.contiguous()
+        rows_ok = qkv.stride(2) == 1 and (B == 1 or qkv.stride(0) == T * qkv.stride(1)) and qkv.stride(1) >= n_out
+        assert rows_ok or not writeback
+        qkv = qkv if rows_ok else qkv.contiguous()
+        ld = qkv.stride(1)
         q = torch.empty(B, T, heads, dim, dtype=qkv.dtype, device=qkv.device)
         qs, nn_, sid = _i32(q_start), _i32(n_new), _i32(seq_ids)
         ck = cache_k if has_kv else q
@@ -106,13 +112,13 @@ def qk_norm_cache_write(qkv: torch.Tensor, cache_k: Optional[torch.Tensor], cach
         qw = q_weight.float().contiguous() if q_weight is not None else None
         kw = k_weight.float().contiguous() if k_weight is not None else None
         cos, sin = rope if rope is not None else (None, None)
-        rc = L.nxd_qk_prep_cache_write(_c.c_int(_code(qkv.dtype)), _lib.ptr(qkv), _c.c_longlong(n_out), _lib.ptr(q),
+        rc = L.nxd_qk_prep_cache_write(_c.c_int(_code(qkv.dtype)), _lib.ptr(qkv), _c.c_longlong(ld), _lib.ptr(q),
                                        _lib.ptr(ck), _lib.ptr(cv), *cargs, _lib.ptr(qs), _lib.ptr(nn_), _lib.ptr(sid),
                                        _c.c_int(B), _c.c_int(T), _c.c_int(heads), _c.c_int(kv_heads), _c.c_int(dim),
                                        _c.c_int(vdim), _c.c_int(int(has_kv)), _c.c_int(int(normalize)), _c.c_float(eps),
                                        _c.c_int(max_pos), _c.c_int(int(writeback and has_kv)), _lib.ptr(qw), _lib.ptr(kw),
                                        _lib.ptr(cos), _lib.ptr(sin), _c.c_int(2 * cos.shape[1] if cos is not None else 0),
-                                       _c.c_int(int(value_from_key)), _lib.stream_ptr())
+                                       _c.c_int(int(value_from_key)), _c.c_int(gv), _lib.stream_ptr())
         _lib.check(rc, "nxd_qk_prep_cache_write", L)
         return q
 
@@ -134,7 +140,7 @@ def qk_norm_cache_write(qkv: torch.Tensor, cache_k: Optional[torch.Tensor], cach
     if has_kv:
         k_raw = qkv[..., heads * dim: (heads + kv_heads) * dim].reshape(B, T, kv_heads, dim)
         k = unit(k_raw, k_weight)
-        v = k_raw if value_from_key else qkv[..., (heads + kv_heads) * dim:].reshape(B, T, kv_heads, vdim)
+        v = k_raw if value_from_key else qkv[..., (heads + kv_heads) * dim:].reshape(B, T, gv, vdim)
         for b in range(B):
             n = T if n_new is None else int(n_new[b])
             line = b if seq_ids is None else int(seq_ids[b])
@@ -156,10 +162,12 @@ def qk_norm_cache_write(qkv: torch.Tensor, cache_k: Optional[torch.Tensor], cach
 def window_attention_ref(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_pos: torch.Tensor, scale: float,
                          window: Optional[int], keep_first: int, slopes: Optional[torch.Tensor],
                          chunk: Optional[int] = None, sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """One sequence in fp32: ``q [Tq, H, D]`` at positions ``q_pos [Tq]`` over keys ``k [G, Tk, D]`` / ``v [G, Tk, Dv]``
-    at positions ``0 .. Tk - 1``."""
+    """One sequence in fp32: ``q [Tq, H, D]`` at positions ``q_pos [Tq]`` over keys ``k [G, Tk, D]`` / ``v [Gv, Tk, Dv]``
+    at positions ``0 .. Tk - 1``; with fewer value heads than key heads, key head ``g`` reads value head ``g % Gv``."""
     H, G = q.shape[1], k.shape[0]
     kf = k.float().repeat_interleave(H // G, dim=0)
+    if v.shape[0] != G:
+        v = v[torch.arange(G, device=v.device) % v.shape[0]]
     vf = v.float().repeat_interleave(H // G, dim=0)
     s = torch.einsum("qhd,hkd->hqk", q.float(), kf) * scale
     j = torch.arange(k.shape[1], device=q.device)
@@ -187,7 +195,7 @@ def window_attention_prefill(q: torch.Tensor, cache_k: torch.Tensor, cache_v: to
                              slopes: Optional[torch.Tensor] = None, n_new: Optional[torch.Tensor] = None,
                              seq_ids: Optional[torch.Tensor] = None, block_table: Optional[torch.Tensor] = None,
                              page_size: int = 0, impl: str = "auto", chunk: Optional[int] = None,
-                             sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
+                             sinks: Optional[torch.Tensor] = None, value_heads: Optional[int] = None) -> torch.Tensor:
     """``impl``: ``auto`` | ``generic`` (fp32-math tile kernel, any sizes) | ``mma`` (bf16 tensor-core kernel, an error
     where it does not apply) -- for tests and measurements.
 
@@ -208,7 +216,8 @@ def window_attention_prefill(q: torch.Tensor, cache_k: torch.Tensor, cache_v: to
                                        _lib.ptr(slopes), _lib.ptr(sk), _c.c_int(B), _c.c_int(T), _c.c_int(H), _c.c_int(G),
                                        _c.c_int(D), _c.c_int(Dv), _c.c_float(scale), _c.c_int(w), _c.c_int(keep_first),
                                        _c.c_int(int(chunk) if chunk else 0),
-                                       _c.c_int({"auto": 0, "generic": 1, "mma": 2}[impl]), _lib.stream_ptr())
+                                       _c.c_int({"auto": 0, "generic": 1, "mma": 2}[impl]),
+                                       _c.c_int(int(value_heads) if value_heads else 0), _lib.stream_ptr())
         _lib.check(rc, "nxd_masked_attn_prefill", L)
         return out
     out = torch.zeros(B, T, H, Dv, dtype=q.dtype, device=q.device)
@@ -230,7 +239,7 @@ def window_attention_decode(q: torch.Tensor, cache_k: torch.Tensor, cache_v: tor
                             slopes: Optional[torch.Tensor] = None, seq_ids: Optional[torch.Tensor] = None,
                             block_table: Optional[torch.Tensor] = None, page_size: int = 0,
                             impl: str = "auto", chunk: Optional[int] = None,
-                            sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
+                            sinks: Optional[torch.Tensor] = None, value_heads: Optional[int] = None) -> torch.Tensor:
     """One new token per row: ``q [B, H, D]`` at ``positions[b]`` -> ``[B, H, Dv]``; only the kept first rows and the
     window's rows of the cache line are read."""
     B, H, D = q.shape
@@ -256,7 +265,8 @@ def window_attention_decode(q: torch.Tensor, cache_k: torch.Tensor, cache_v: tor
                                       _lib.ptr(out), _lib.ptr(pos), _lib.ptr(sid), _lib.ptr(slopes), _lib.ptr(sk),
                                       _c.c_int(B), _c.c_int(H), _c.c_int(G), _c.c_int(D), _c.c_int(Dv), _c.c_float(scale),
                                       _c.c_int(w), _c.c_int(keep_first), _c.c_int(int(chunk) if chunk else 0),
-                                      _c.c_int({"auto": 0, "generic": 1, "mma": 2}[impl]), _lib.stream_ptr())
+                                      _c.c_int({"auto": 0, "generic": 1, "mma": 2}[impl]),
+                                      _c.c_int(int(value_heads) if value_heads else 0), _lib.stream_ptr())
         _lib.check(rc, "nxd_masked_attn_decode", L)
         return out
     out = torch.empty(B, H, Dv, dtype=q.dtype, device=q.device)
@@ -268,6 +278,30 @@ def window_attention_decode(q: torch.Tensor, cache_k: torch.Tensor, cache_v: tor
         out[b] = window_attention_ref(q[b:b + 1], kk, vv, torch.tensor([p], device=q.device), scale, w, keep_first,
                                       slopes, chunk, sinks)[0].to(q.dtype)
     return out
+
+
+def diff_attention_combine(maps: torch.Tensor, lq1: torch.Tensor, lk1: torch.Tensor, lq2: torch.Tensor,
+                           lk2: torch.Tensor, diff: float, eps: float) -> torch.Tensor:
+    """Differential attention: ``maps [N, 2 * H, Dv]`` holds two softmax attention maps over the same values (heads
+    ``0 .. H-1``: map 1, ``H .. 2H-1``: map 2) -> ``[N, H * Dv]``: ``o = a1 - lambda a2`` with
+    ``lambda = exp(<lq1, lk1>) - exp(<lq2, lk2>) + diff`` (one number, fp32), every head divided by its root mean square
+    (``eps`` inside the root), times ``1 - diff``."""
+    N, H2, Dv = maps.shape
+    H = H2 // 2
+    if _use_kernel(maps):
+        maps = maps if maps.is_contiguous() else maps.contiguous()
+        out = torch.empty(N, H * Dv, dtype=maps.dtype, device=maps.device)
+        L = _lib.lib(GROUP)
+        rc = L.nxd_diff_attn_combine(_c.c_int(_code(maps.dtype)), _lib.ptr(maps), _lib.ptr(out), _lib.ptr(lq1),
+                                     _lib.ptr(lk1), _lib.ptr(lq2), _lib.ptr(lk2), _c.c_longlong(N), _c.c_int(H),
+                                     _c.c_int(Dv), _c.c_int(lq1.numel()), _c.c_float(diff), _c.c_float(eps),
+                                     _lib.stream_ptr())
+        _lib.check(rc, "nxd_diff_attn_combine", L)
+        return out
+    lam = torch.exp((lq1.float() * lk1.float()).sum()) - torch.exp((lq2.float() * lk2.float()).sum()) + diff
+    o = maps[:, :H].float() - lam * maps[:, H:].float()
+    o = o / torch.sqrt(o.pow(2).mean(-1, keepdim=True) + eps) * (1.0 - diff)
+    return o.reshape(N, H * Dv).to(maps.dtype)
 
 
 def tc_prefill_applies(q: torch.Tensor, dim: int, vdim: int, n_out: int) -> bool:
