@@ -362,3 +362,13 @@ class RasodraRunner(InferenceRunner):
 
         kw.setdefault("model_cls", RasodraInferenceModel)
         super().__init__(*a, **kw)
+
+
+class GogalixRunner(InferenceRunner):
+    """Runner of the Gogalix family (``models/gogalix.py``): same buckets, graphs and generate loop."""
+
+    def __init__(self, *a, **kw):
+        from .hybrid import GogalixInferenceModel
+
+        kw.setdefault("model_cls", GogalixInferenceModel)
+        super().__init__(*a, **kw)

@@ -9,3 +9,5 @@ from .dbrx import DbrxConfig, DbrxForCausalLM, convert_dbrx_hf_state_dict, dbrx_
 from .gekazen import GekazenConfig, GekazenForCausalLM, convert_gekazen_state_dict, tiny_gekazen  # noqa: F401
 from .rasodra import (RasodraConfig, RasodraForCausalLM, convert_rasodra_state_dict, export_rasodra_state_dict,  # noqa: F401
                       tiny_rasodra)
+from .gogalix import (GogalixConfig, GogalixForCausalLM, convert_gogalix_state_dict, export_gogalix_state_dict,  # noqa: F401
+                      tiny_gogalix)
