@@ -148,43 +148,144 @@ __device__ __forceinline__ float ld_any(const void* p, int is_f32, long long i) 
     return is_f32 ? reinterpret_cast<const float*>(p)[i] : __bfloat162float(reinterpret_cast<const bf16*>(p)[i]);
 }
 
-template <typename TH>
+__device__ __forceinline__ void ld4_any(const void* p, int is_f32, long long i, float (&v)[4]) {
+    if (is_f32) {
+        const float4 t = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + i);
+        v[0] = t.x, v[1] = t.y, v[2] = t.z, v[3] = t.w;
+    } else {
+        const uint2 t = *reinterpret_cast<const uint2*>(reinterpret_cast<const bf16*>(p) + i);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const bf162*>(&t.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const bf162*>(&t.y));
+        v[0] = a.x, v[1] = a.y, v[2] = b.x, v[3] = b.y;
+    }
+}
+__device__ __forceinline__ void ld4_vec(const float* p, int c, float (&v)[4]) {
+    if (p == nullptr) {
+        v[0] = v[1] = v[2] = v[3] = 0.f;
+        return;
+    }
+    const float4 t = *reinterpret_cast<const float4*>(p + c);
+    v[0] = t.x, v[1] = t.y, v[2] = t.z, v[3] = t.w;
+}
+__device__ __forceinline__ void st4(float* p, const float (&v)[4]) { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+__device__ __forceinline__ void st4(bf16* p, const float (&v)[4]) {
+    uint2 t;
+    *reinterpret_cast<bf162*>(&t.x) = __floats2bfloat162_rn(v[0], v[1]);
+    *reinterpret_cast<bf162*>(&t.y) = __floats2bfloat162_rn(v[2], v[3]);
+    *reinterpret_cast<uint2*>(p) = t;
+}
+
+// VEC = 4: four consecutive columns per thread and iteration through 8- / 16-byte accesses (widths, gate offsets and
+// pitches that are multiples of 4); VEC = 1: any sizes.
+template <typename TH, int VEC>
 __global__ void __launch_bounds__(PN_THREADS)
 gated_residual_norm_kernel(float* __restrict__ x, const void* __restrict__ y1, int y1_f32, const void* __restrict__ y2,
                            int y2_f32, const float* __restrict__ y2_bias, const void* __restrict__ gate, int gate_f32,
                            long long ld_g, int off1, int off2, const float* __restrict__ gb1,
                            const float* __restrict__ gb2, const float* __restrict__ ls1, const float* __restrict__ ls2,
                            const float* __restrict__ w_next, TH* __restrict__ h, int W, float eps) {
-    extern __shared__ float rowbuf[];
+    extern __shared__ __align__(16) float rowbuf[];
     __shared__ float red[32];
     const long long row = blockIdx.x;
     float* xr = x + row * W;
     float ss = 0.f;
-    for (int c = threadIdx.x; c < W; c += PN_THREADS) {
-        float v = xr[c];
-        if (y1 != nullptr) {
-            float z = gate != nullptr ? ld_any(gate, gate_f32, row * ld_g + off1 + c) + (gb1 != nullptr ? gb1[c] : 0.f) : 0.f;
-            float a = ld_any(y1, y1_f32, row * W + c) * (ls1 != nullptr ? ls1[c] : 1.f);
-            if (gate != nullptr) a *= 1.f / (1.f + expf(-z));
-            if (y2 != nullptr) {
-                float f = (ld_any(y2, y2_f32, row * W + c) + (y2_bias != nullptr ? y2_bias[c] : 0.f)) *
-                          (ls2 != nullptr ? ls2[c] : 1.f);
-                if (gate != nullptr) {
-                    z = ld_any(gate, gate_f32, row * ld_g + off2 + c) + (gb2 != nullptr ? gb2[c] : 0.f);
-                    f *= 1.f / (1.f + expf(-z));
+    if (VEC == 4) {
+        for (int c = threadIdx.x * 4; c < W; c += PN_THREADS * 4) {
+            float v[4];
+            ld4_vec(xr, c, v);
+            if (y1 != nullptr) {
+                float a[4], z[4], t[4];
+                ld4_any(y1, y1_f32, row * W + c, a);
+                if (ls1 != nullptr) {
+                    ld4_vec(ls1, c, t);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) a[i] *= t[i];
                 }
-                a += f;
+                if (gate != nullptr) {
+                    ld4_any(gate, gate_f32, row * ld_g + off1 + c, z);
+                    ld4_vec(gb1, c, t);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) a[i] *= 1.f / (1.f + expf(-(z[i] + t[i])));
+                }
+                if (y2 != nullptr) {
+                    float f[4];
+                    ld4_any(y2, y2_f32, row * W + c, f);
+                    ld4_vec(y2_bias, c, t);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) f[i] += t[i];
+                    if (ls2 != nullptr) {
+                        ld4_vec(ls2, c, t);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) f[i] *= t[i];
+                    }
+                    if (gate != nullptr) {
+                        ld4_any(gate, gate_f32, row * ld_g + off2 + c, z);
+                        ld4_vec(gb2, c, t);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) f[i] *= 1.f / (1.f + expf(-(z[i] + t[i])));
+                    }
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) a[i] += f[i];
+                }
+#pragma unroll
+                for (int i = 0; i < 4; ++i) v[i] += a[i];
+                st4(xr + c, v);
             }
-            v += a;
-            xr[c] = v;
+            st4(rowbuf + c, v);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) ss = fmaf(v[i], v[i], ss);
         }
-        rowbuf[c] = v;
-        ss = fmaf(v, v, ss);
+    } else {
+        for (int c = threadIdx.x; c < W; c += PN_THREADS) {
+            float v = xr[c];
+            if (y1 != nullptr) {
+                float z = gate != nullptr ? ld_any(gate, gate_f32, row * ld_g + off1 + c) + (gb1 != nullptr ? gb1[c] : 0.f) : 0.f;
+                float a = ld_any(y1, y1_f32, row * W + c) * (ls1 != nullptr ? ls1[c] : 1.f);
+                if (gate != nullptr) a *= 1.f / (1.f + expf(-z));
+                if (y2 != nullptr) {
+                    float f = (ld_any(y2, y2_f32, row * W + c) + (y2_bias != nullptr ? y2_bias[c] : 0.f)) *
+                              (ls2 != nullptr ? ls2[c] : 1.f);
+                    if (gate != nullptr) {
+                        z = ld_any(gate, gate_f32, row * ld_g + off2 + c) + (gb2 != nullptr ? gb2[c] : 0.f);
+                        f *= 1.f / (1.f + expf(-z));
+                    }
+                    a += f;
+                }
+                v += a;
+                xr[c] = v;
+            }
+            rowbuf[c] = v;
+            ss = fmaf(v, v, ss);
+        }
     }
     if (w_next == nullptr || h == nullptr) return;
     const float r = w_next[0] / sqrtf(block_sum(ss, red) / (float)W + eps);
     TH* hr = h + row * W;
-    for (int c = threadIdx.x; c < W; c += PN_THREADS) stf(hr + c, rowbuf[c] * r);
+    if (VEC == 4) {
+        for (int c = threadIdx.x * 4; c < W; c += PN_THREADS * 4) {
+            float v[4];
+            ld4_vec(rowbuf, c, v);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) v[i] *= r;
+            st4(hr + c, v);
+        }
+    } else {
+        for (int c = threadIdx.x; c < W; c += PN_THREADS) stf(hr + c, rowbuf[c] * r);
+    }
+}
+
+template <typename TH, int VEC>
+int launch_gated(float* x, const void* y1, int y1_dtype, const void* y2, int y2_dtype, const float* y2_bias,
+                 const void* gate, int gate_dtype, long long ld_g, int off1, int off2, const float* gb1, const float* gb2,
+                 const float* ls1, const float* ls2, const float* w_next, void* h, long long rows, int W, float eps,
+                 cudaStream_t st) {
+    const size_t smem = (size_t)W * sizeof(float);
+    auto kern = gated_residual_norm_kernel<TH, VEC>;
+    if (smem > 48 * 1024) NXD_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<(unsigned)rows, PN_THREADS, smem, st>>>(x, y1, y1_dtype, y2, y2_dtype, y2_bias, gate, gate_dtype, ld_g, off1, off2,
+                                                   gb1, gb2, ls1, ls2, w_next, (TH*)h, W, eps);
+    NXD_LAUNCH_CHECK();
+    return 0;
 }
 
 }  // namespace
@@ -200,22 +301,21 @@ NXD_API int nxd_gated_residual_norm(float* x, const void* y1, int y1_dtype, cons
                                     void* stream) {
     if (rows == 0) return 0;
     NXD_REQUIRE(rows < (1ll << 31), "gated residual: %lld rows", rows);
-    const size_t smem = (size_t)W * sizeof(float);
-    NXD_REQUIRE(smem <= 200 * 1024, "gated residual: width %d", W);
+    NXD_REQUIRE((size_t)W * sizeof(float) <= 200 * 1024, "gated residual: width %d", W);
     cudaStream_t st = (cudaStream_t)stream;
+    auto al = [](const void* p, size_t n) { return p == nullptr || ((uintptr_t)p % n) == 0; };
+    const bool vec = W % 4 == 0 && ld_g % 4 == 0 && off1 % 4 == 0 && off2 % 4 == 0 && al(x, 16) && al(y1, 16) && al(y2, 16) &&
+                     al(gate, 16) && al(h, 16) && al(y2_bias, 16) && al(gb1, 16) && al(gb2, 16) && al(ls1, 16) && al(ls2, 16);
+#define NXD_GR(TH, V)                                                                                                  \
+    return launch_gated<TH, V>(x, y1, y1_dtype, y2, y2_dtype, y2_bias, gate, gate_dtype, ld_g, off1, off2, gb1, gb2, ls1, \
+                               ls2, w_next, h, rows, W, eps, st)
     if (h_dtype == 0) {
-        auto kern = gated_residual_norm_kernel<bf16>;
-        if (smem > 48 * 1024) NXD_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        kern<<<(unsigned)rows, PN_THREADS, smem, st>>>(x, y1, y1_dtype, y2, y2_dtype, y2_bias, gate, gate_dtype, ld_g, off1,
-                                                       off2, gb1, gb2, ls1, ls2, w_next, (bf16*)h, W, eps);
-    } else {
-        auto kern = gated_residual_norm_kernel<float>;
-        if (smem > 48 * 1024) NXD_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        kern<<<(unsigned)rows, PN_THREADS, smem, st>>>(x, y1, y1_dtype, y2, y2_dtype, y2_bias, gate, gate_dtype, ld_g, off1,
-                                                       off2, gb1, gb2, ls1, ls2, w_next, (float*)h, W, eps);
+        if (vec) NXD_GR(bf16, 4);
+        NXD_GR(bf16, 1);
     }
-    NXD_LAUNCH_CHECK();
-    return 0;
+    if (vec) NXD_GR(float, 4);
+    NXD_GR(float, 1);
+#undef NXD_GR
 }
 
 // y [rows, W] (y_dtype), w [W] (w_dtype), x [rows, W] fp32 or NULL, h [rows, W] (h_dtype) or NULL; dtypes: 0 bf16,

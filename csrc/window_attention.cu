@@ -481,7 +481,7 @@ int launch_prefill_mma(const void* q, const void* ck, const void* cv, CacheAddr 
                        int G, float scale, int window, int keep_first, int chunk, const float* sinks, cudaStream_t st) {
     const size_t smem = (size_t)(MQ * (D + 8) + 2 * MK * (D + 8) + 2 * MK * (DV + 8)) * sizeof(bf16);
     auto kern = window_attn_prefill_mma_kernel<D, DV>;
-    if (smem > 48 * 1024) NXD_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    if (smem > 32 * 1024) NXD_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid((Tn + MQ - 1) / MQ, H, B);
     kern<<<grid, M_THREADS, smem, st>>>((const bf16*)q, (const bf16*)ck, (const bf16*)cv, ka, va, (bf16*)out, q_start,
                                         n_new, seq_ids, slopes, Tn, H, G, scale, window, keep_first, chunk, sinks);
@@ -821,7 +821,7 @@ int launch_decode_mma(const void* q, const void* ck, const void* cv, CacheAddr k
     static_assert(DV % VS == 0 && VS % 16 == 0, "value slices");
     const size_t smem = (size_t)(DM_ROWS * (D + 8) + 2 * MK * (D + 8) + 2 * MK * (VS + 8)) * sizeof(bf16);
     auto kern = window_attn_decode_mma_kernel<D, DV, VS, (D > 256)>;
-    if (smem > 48 * 1024) NXD_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    if (smem > 32 * 1024) NXD_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid(G * groups, B, DV / VS);
     kern<<<grid, DM_THREADS, smem, st>>>((const bf16*)q, (const bf16*)ck, (const bf16*)cv, ka, va, (bf16*)out, positions,
                                          seq_ids, slopes, H, G, scale, window, keep_first, chunk, sinks, groups);
@@ -879,7 +879,7 @@ int launch_prefill(const void* q, const void* ck, const void* cv, CacheAddr ka, 
                    cudaStream_t st) {
     const size_t smem = (size_t)(BQ * D + BK * (D + 1) + BK * Dv + BQ * BK) * sizeof(float);
     auto kern = window_attn_prefill_kernel<T>;
-    if (smem > 48 * 1024) NXD_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    if (smem > 32 * 1024) NXD_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid((Tn + BQ - 1) / BQ, H, B);
     kern<<<grid, PF_THREADS, smem, st>>>((const T*)q, (const T*)ck, (const T*)cv, ka, va, (T*)out, q_start, n_new,
                                          seq_ids, slopes, Tn, H, G, D, Dv, scale, window, keep_first, chunk, sinks);
@@ -895,7 +895,7 @@ int launch_decode_rm(const void* q, const void* ck, const void* cv, CacheAddr ka
     const int groups = (R_all + DEC_R - 1) / DEC_R;
     const size_t smem = (size_t)(DEC_R * D + DEC_WARPS * DEC_R * (Dv + 2)) * sizeof(float);
     auto kern = window_attn_decode_kernel<T, DEC_R, DEC_MV>;
-    if (smem > 48 * 1024) NXD_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    if (smem > 32 * 1024) NXD_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid(G * groups, B);
     kern<<<grid, DEC_WARPS * 32, smem, st>>>((const T*)q, (const T*)ck, (const T*)cv, ka, va, (T*)out, positions, seq_ids,
                                              slopes, H, G, D, Dv, scale, window, keep_first, chunk, sinks, groups);
@@ -1004,6 +1004,10 @@ NXD_API int nxd_masked_attn_prefill(int dtype, const void* q, const void* cache_
         NXD_WA_CASE(128, 64);
         NXD_WA_CASE(96, 64);      // key size = un-rotated + rotated dimensions of an expanded latent head
         NXD_WA_CASE(192, 128);
+        NXD_WA_CASE(32, 64);      // two attention maps of half the value size (differential attention)
+        NXD_WA_CASE(48, 96);
+        NXD_WA_CASE(96, 192);
+        NXD_WA_CASE(128, 256);
 #undef NXD_WA_CASE
     }
     NXD_REQUIRE(impl != 2, "attention: no tensor-core kernel for bf16=%d D=%d Dv=%d", dtype == 0, D, Dv);
@@ -1054,6 +1058,10 @@ NXD_API int nxd_masked_attn_decode(int dtype, const void* q, const void* cache_k
         NXD_WD_CASE(64, 128);
         NXD_WD_CASE(128, 64);
         NXD_WD_CASE(160, 128);    // latent rows: compressed key/value + shared rotated key part; value = the compressed part
+        NXD_WD_CASE(32, 64);      // two attention maps of half the value size (differential attention)
+        NXD_WD_CASE(48, 96);
+        NXD_WD_CASE(96, 192);
+        NXD_WD_CASE(128, 256);
 #undef NXD_WD_CASE
         if (D == 288 && Dv == 256)                   // wide latent rows: the value columns are split over CTAs
             return launch_decode_mma<288, 256, 128>(q, cache_k, cache_v, ka, va, out, positions, seq_ids, slopes, B, H, G,

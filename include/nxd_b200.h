@@ -381,8 +381,8 @@ int nxd_delta_prep(int dtype, const void* proj, long long ld, int off_q, int off
 int nxd_delta_conv_state(int dtype, const void* proj, long long ld, int off_q, int off_k, int off_v, float* conv_state,
                          const int* q_start, const int* n_new, const int* seq_ids, int B, int Tn, int H, int G, int D,
                          int Dv, int taps, void* stream);
-int nxd_delta_scan(const float* qn, const float* kn, const float* vn, const float* apre, long long ld_a, int a_off,
-                   const float* bpre, long long ld_b, int b_off, const float* a_log, const float* dt_bias, float* S,
+int nxd_delta_scan(const float* qn, const float* kn, const float* vn, float* apre, long long ld_a, int a_off,
+                   float* bpre, long long ld_b, int b_off, const float* a_log, const float* dt_bias, float* S,
                    float* out, const int* q_start, const int* n_new, const int* seq_ids, int B, int Tn, int H, int G, int D,
                    int Dv, int per_channel, void* stream);
 /* gate and up columns of a wider row (+ fp32 biases or NULL) -> gated activation as in nxd_clamped_glu, out [rows, F] */

@@ -18,6 +18,7 @@ import torch
 from ..models.gekazen import GekazenConfig
 from ..models.mixtral import MixtralConfig
 from ..ops import _lib
+from ..ops import activation as act_ops
 from ..ops import attention as attn_ops
 from ..ops import moe_sparse  # noqa: F401
 from ..ops import norm as norm_ops
@@ -405,5 +406,187 @@ def run_hybrid(steps: int = 10, warmup: int = 3, device=None, sizes=None) -> dic
     for s in (sizes or HYBRID_SIZES):
         out["cases"].append(hybrid_serve_case(s, steps, warmup, dev))
         out["kernels"][s["name"]] = hybrid_kernel_cases(s, steps, warmup, dev)
+    out["gpu_launches"] = _lib.kernel_launches() - before
+    return out
+
+
+# ---- Gogalix (gated delta rule + differential window attention on a gated parallel residual) next to the closest existing
+# family, Rasodra (recurrent matrix memory + attention over the cache, fp32 stream), at equal width, heads, head size,
+# layer count and feed-forward parameters ---------------------------------------------------------------------------------
+def gogalix_config(s: dict):
+    from ..models.gogalix import GogalixConfig
+
+    # three matrices of (width x f) against Rasodra's two of (width x ff): f = 2/3 ff keeps the parameters equal
+    ff = {"kind": "dense", "ff": (2 * s["ff"] // 3 + 127) // 128 * 128}
+    half = s["dim"] // 2                        # two maps of half the head size: the query / key rows of a plain head
+    att = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": half, "vdim": s["dim"], "scale": half ** -0.5,
+           "diff": 0.5, "mask": {"size": s["chunk"]}}
+    rec = {"heads": s["rec_heads"], "kv_heads": s["rec_heads"], "dim": s["rec_dim"], "vdim": s["rec_vdim"], "conv": 4}
+    return GogalixConfig.from_dict({
+        "architecture": "Gogalix", "vocab": VOCAB, "width": s["width"], "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
+        "layers": [{"type": "attention", "mixer": att, "mlp": ff},
+                   {"type": "delta", "mixer": rec, "mlp": None},
+                   {"type": "attention", "mixer": dict(att, kv_from=0), "mlp": ff},
+                   {"type": "channel_delta", "mixer": dict(rec, rank=64), "mlp": ff}]}, torch_dtype=torch.bfloat16)
+
+
+def delta_serve_case(s: dict, steps: int, warmup: int, dev) -> dict:
+    from .hybrid import GogalixInferenceModel, RasodraInferenceModel
+
+    timer = _Timer(dev)
+    out = {"size": dict(s)}
+    ic = dict(batch_size=s["decode_batch"], max_batch_size=s["decode_batch"], max_context_length=s["prompt"],
+              seq_len=s["prompt"] + 64, is_continuous_batching=True, use_cuda_graphs=False)
+    for name, make in (("gogalix", lambda: GogalixInferenceModel(gogalix_config(s), InferenceConfig(**ic), device=dev)),
+                       ("rasodra", lambda: RasodraInferenceModel(rasodra_config(s), InferenceConfig(**ic), device=dev))):
+        torch.manual_seed(0)
+        model = make()
+        model.init_kv_cache(device=dev)
+        out[name] = _serve(model, s, timer, steps, warmup, dev)
+        del model
+        torch.cuda.empty_cache()
+    out["gogalix_over_rasodra"] = {k: out["gogalix"][k] / out["rasodra"][k]
+                                   for k in ("prefill_tokens_per_s", "decode_tokens_per_s")}
+    return out
+
+
+def delta_kernel_cases(s: dict, steps: int, warmup: int, dev) -> List[dict]:
+    """Gogalix's own kernels on the shapes of ``s``, alone, with roofline fractions, each next to the like kernel of the
+    Rasodra family (recurrent scan / step, attention over the cache, norm chain, projection epilogue)."""
+    from ..ops import delta_rule as dr
+    from ..ops import mlstm as ml
+
+    pk = peaks()
+    timer = _Timer(dev)
+    bf = torch.bfloat16
+    B, T, H, G, D, W, Bd = s["prefill_batch"], s["prompt"], s["heads"], s["kv_heads"], s["dim"], s["width"], s["decode_batch"]
+    rows = []
+
+    def row(kernel, like, ms, flops=None, nbytes=None):
+        r = {"kernel": kernel, "like": like, "ms": ms, "peak": pk["source"]}
+        if flops is not None:
+            r["tflops"] = flops / ms / 1e9
+            r["of_peak"] = r["tflops"] / pk["bf16_tflops"]
+        if nbytes is not None:
+            r["gbs"] = nbytes / ms / 1e6
+            r["of_peak"] = r["gbs"] / pk["hbm_gbs"]
+        rows.append(r)
+
+    S, N = T + 64, B * T
+    zero = torch.zeros(B, dtype=torch.int32, device=dev)
+    win = s["chunk"]
+    i = torch.arange(T).reshape(T, 1)
+    j = torch.arange(T).reshape(1, T)
+    pairs_win = int(((j <= i) & (i - j < win)).sum())
+    pairs_chunk = int(((j <= i) & (i // win == j // win)).sum())
+    # differential attention: 2H query heads of D/2 over 2G key heads and G value heads of D
+    Dh = D // 2
+    q2 = torch.randn(B, T, 2 * H, Dh, device=dev, dtype=bf)
+    ck2 = torch.randn(max(B, Bd), 2 * G, S, Dh, device=dev, dtype=bf)
+    cv2 = torch.randn(max(B, Bd), G, S, D, device=dev, dtype=bf)
+    ms = timer(lambda: wa.window_attention_prefill(q2, ck2, cv2, zero, Dh ** -0.5, win, value_heads=G), steps, warmup)
+    row("differential attention prefill (two maps as heads, window, over the cache)", "prefill attention", ms,
+        flops=2.0 * (Dh + D) * pairs_win * 2 * H * B)
+    q1 = torch.randn(B, T, H, D, device=dev, dtype=bf)
+    ck1 = torch.randn(max(B, Bd), G, S, D, device=dev, dtype=bf)
+    ms = timer(lambda: wa.window_attention_prefill(q1, ck1, cv2, zero, D ** -0.5, chunk=win), steps, warmup)
+    row("chunked attention prefill over the cache (the like kernel)", "prefill attention", ms,
+        flops=4.0 * D * pairs_chunk * H * B)
+    qd2 = torch.randn(Bd, 2 * H, Dh, device=dev, dtype=bf)
+    posd = torch.full((Bd,), T, dtype=torch.int32, device=dev)
+    seen = min(win, T + 1)
+    ms = timer(lambda: wa.window_attention_decode(qd2, ck2, cv2, posd, Dh ** -0.5, win, value_heads=G), steps, warmup)
+    row("differential attention decode (rows of the window; values read by both maps)", "decode attention", ms,
+        nbytes=2.0 * seen * G * (2 * Dh + D) * Bd)
+    qd1 = torch.randn(Bd, H, D, device=dev, dtype=bf)
+    posm = torch.full((Bd,), T - 1, dtype=torch.int32, device=dev)
+    ms = timer(lambda: wa.window_attention_decode(qd1, ck1, cv2, posm, D ** -0.5, chunk=win), steps, warmup)
+    row("chunked attention decode, a full chunk (the like kernel)", "decode attention", ms,
+        nbytes=2.0 * ((T - 1) % win + 1) * G * 2 * D * Bd)
+    maps = torch.randn(N, 2 * H, D, device=dev, dtype=bf)
+    lv = [torch.randn(Dh, device=dev) * 0.1 for _ in range(4)]
+    ms = timer(lambda: wa.diff_attention_combine(maps, *lv, 0.5, 1e-6), steps, warmup)
+    row("a1 - lambda a2 + head norm", "norm", ms, nbytes=2.0 * N * 3 * H * D)
+    wide = torch.randn(B, T, 2 * H * Dh + 2 * G * Dh + G * D, device=dev, dtype=bf)
+    ckw, cvw = torch.zeros(B, 2 * G, S, Dh, device=dev, dtype=bf), torch.zeros(B, G, S, D, device=dev, dtype=bf)
+    ms = timer(lambda: wa.qk_norm_cache_write(wide, ckw, cvw, zero, 2 * H, 2 * G, Dh, D, 1e-6, normalize=False,
+                                              value_heads=G), steps, warmup)
+    row("query copy + cache write of both maps", "projection epilogue", ms, nbytes=2.0 * N * (4 * H * Dh + 4 * G * Dh + 2 * G * D))
+    del q2, ck2, cv2, q1, ck1, maps, wide, ckw, cvw
+    # gated delta rule
+    Hr, Dk, Dvr, taps = s["rec_heads"], s["rec_dim"], s["rec_vdim"], 4
+    C = 2 * Hr * Dk + Hr * Dvr
+    proj = torch.randn(B, T, C, device=dev, dtype=bf) * 0.3
+    cw = torch.randn(C, taps, device=dev) * 0.3
+    cst = torch.zeros(max(B, Bd), taps - 1, C, device=dev)
+    ms = timer(lambda: dr.delta_prep(proj, (0, Hr * Dk, 2 * Hr * Dk), cw, cst, zero, Hr, Hr, Dk, Dvr, Dk ** -0.5), steps, warmup)
+    row("short convolution + silu + unit norm + convolution state", "projection epilogue", ms, nbytes=float(N * C * (2 + 4)))
+    qn, kn, vn = dr.delta_prep(proj, (0, Hr * Dk, 2 * Hr * Dk), cw, cst, zero, Hr, Hr, Dk, Dvr, Dk ** -0.5)
+    St = torch.zeros(max(B, Bd), Hr, Dk, Dvr, device=dev)
+    a_log = torch.full((Hr,), -3.0, device=dev)
+    for per_channel in (False, True):
+        na = Hr * Dk if per_channel else Hr
+        apre, bpre, dtb = torch.randn(N, na, device=dev), torch.randn(N, Hr, device=dev), torch.zeros(na, device=dev)
+        tag = "one decay per key channel" if per_channel else "one decay per head"
+        ms = timer(lambda: dr.delta_scan(qn, kn, vn, apre, 0, bpre, 0, a_log, dtb, St, zero, per_channel), steps, warmup)
+        row(f"gated delta rule, prompt, {tag} (token by token, state slice in registers)", "prefill attention", ms,
+            flops=6.0 * Dk * Dvr * Hr * B * T)
+        one = torch.ones(Bd, dtype=torch.int32, device=dev)
+        qd, kd, vd = (x[:1].expand(Bd, *x.shape[1:])[:, :1].contiguous() for x in (qn, kn, vn))
+        ms = timer(lambda: dr.delta_scan(qd, kd, vd, apre[:Bd], 0, bpre[:Bd], 0, a_log, dtb, St, one, per_channel), steps, warmup)
+        row(f"gated delta rule, one token, {tag} (state read + written)", "decode attention", ms,
+            nbytes=8.0 * Dk * Dvr * Hr * Bd)
+    ld = 2 * Hr * Dk + 2 * Hr * Dvr
+    pr = torch.randn(B, T, ld, device=dev, dtype=bf) * 0.3
+    gi, gf = torch.randn(N, Hr, device=dev), -torch.rand(N, Hr, device=dev) * 0.1
+    st = (torch.zeros(Bd, Hr, Dk, Dvr, device=dev), torch.zeros(Bd, Hr, Dk, device=dev), torch.zeros(Bd, Hr, device=dev))
+    ms = timer(lambda: ml.mlstm_scan(pr, (0, Hr * Dk, 2 * Hr * Dk), gi, gf, st, zero, Hr, Dk, Dvr, Dk ** -0.5), steps, warmup)
+    row("matrix-memory scan, prompt, token by token (the like kernel)", "prefill attention", ms, flops=4.0 * Dk * Dvr * Hr * B * T)
+    ms = timer(lambda: ml.mlstm_chunkwise(pr, (0, Hr * Dk, 2 * Hr * Dk), gi, gf, st, zero, Hr, Dk, Dvr, Dk ** -0.5), steps,
+               warmup)
+    row("matrix-memory prompt, chunk-wise (the like kernel of long bf16 steps)", "prefill attention", ms,
+        flops=4.0 * Dk * Dvr * Hr * B * T)
+    prd = torch.randn(Bd, 1, ld, device=dev, dtype=bf) * 0.3
+    one = torch.ones(Bd, dtype=torch.int32, device=dev)
+    ms = timer(lambda: ml.mlstm_scan(prd, (0, Hr * Dk, 2 * Hr * Dk), gi[:Bd], gf[:Bd], st, one, Hr, Dk, Dvr, Dk ** -0.5),
+               steps, warmup)
+    row("matrix-memory scan, one token (the like kernel)", "decode attention", ms, nbytes=8.0 * Dk * Dvr * Hr * Bd)
+    o = torch.randn(N, Hr, Dvr, device=dev)
+    gsrc = torch.randn(N, Hr * Dvr, device=dev, dtype=bf)
+    wn = torch.ones(Hr * Dvr, device=dev)
+    ms = timer(lambda: ml.head_norm_gate(o, gsrc, 0, Hr, Dvr, wn, 1e-6, True, bf, gate_act="silu"), steps, warmup)
+    row("head norm * weight * silu gate", "norm", ms, nbytes=float(N * Hr * Dvr * (4 + 2 + 2)))
+    del proj, qn, kn, vn, pr, o, gsrc
+    # the residual update
+    x32 = torch.randn(N, W, device=dev)
+    y1, y2 = torch.randn(N, W, device=dev, dtype=bf), torch.randn(N, W, device=dev, dtype=bf)
+    gate = torch.randn(N, 2 * W, device=dev, dtype=bf)
+    vecs = [torch.randn(W, device=dev) for _ in range(5)]
+    wnext = torch.ones(1, device=dev)
+    ms = timer(lambda: norm_ops.gated_residual_norm_(x32, y1, y2, vecs[0], gate, (0, W), vecs[1], vecs[2], vecs[3], vecs[4],
+                                                     wnext, 1e-6, bf), steps, warmup)
+    row("gated residual of both sublayers + layer scale + next norm", "norm", ms, nbytes=float(N * W * (4 + 4 + 2 + 2 + 4 + 2)))
+    w1, w2 = torch.ones(W, device=dev), torch.ones(W, device=dev)
+    ms = timer(lambda: norm_ops.norm_chain_(x32, y1, w1, w2, 1e-6, bf), steps, warmup)
+    row("post-norm + fp32 residual + next pre-norm (the like kernel)", "norm", ms, nbytes=float(N * W * (2 + 4 + 4 + 2)))
+    F = (2 * s["ff"] // 3 + 127) // 128 * 128
+    src = torch.randn(N, 2 * F, device=dev, dtype=bf)
+    gb, ub = torch.zeros(F, device=dev), torch.zeros(F, device=dev)
+    ms = timer(lambda: moe_sparse.glu_bias(src, 0, F, F, gb, ub), steps, warmup)
+    row("silu(gate + b) * (up + b) from the fused projection", "activation", ms, nbytes=2.0 * N * 3 * F)
+    ms = timer(lambda: act_ops.swiglu(src), steps, warmup)
+    row("swiglu (the like kernel of the Llama decoder)", "activation", ms, nbytes=2.0 * N * 3 * F)
+    return rows
+
+
+def run_delta(steps: int = 10, warmup: int = 3, device=None, sizes=None) -> dict:
+    dev = device or torch.device("cuda", torch.cuda.current_device())
+    before = _lib.kernel_launches()
+    out = {"metric": "Gogalix vs Rasodra, serving throughput at equal layer sizes", "dtype": "bf16",
+           "data": "synthetic token ids, random-init weights", "steps": steps, "warmup": max(warmup, 3),
+           "l2": "192 MB written between timed runs", "peaks": peaks(), "cases": [], "kernels": {}}
+    for s in (sizes or HYBRID_SIZES):
+        out["cases"].append(delta_serve_case(s, steps, warmup, dev))
+        out["kernels"][s["name"]] = delta_kernel_cases(s, steps, warmup, dev)
     out["gpu_launches"] = _lib.kernel_launches() - before
     return out

@@ -118,7 +118,8 @@ def delta_scan(qn: torch.Tensor, kn: torch.Tensor, vn: torch.Tensor, a_pre: torc
     pre-activations at column ``a_offset + h`` (or ``a_offset + h * dim + i`` with ``per_channel``), ``b_pre [B * T, ldb]``
     fp32 the beta pre-activations at ``b_offset + h``; ``a_log [H]``, ``dt_bias [H]`` or ``[H * dim]`` fp32;
     ``S [lines, H, dim, vdim]`` fp32, updated in place for line ``seq_ids[b]`` (default ``b``).  Tokens ``t >= n_new[b]``
-    are padding: they leave the state alone and come out as zeros.  Returns fp32 ``o [B, T, H, vdim]``."""
+    are padding: they leave the state alone and come out as zeros.  On the GPU ``a_pre`` and ``b_pre`` are overwritten
+    with the decay factors and beta.  Returns fp32 ``o [B, T, H, vdim]``."""
     B, T, G, D = qn.shape
     H, Dv = vn.shape[2], vn.shape[3]
     if qn.is_cuda and _lib.available(GROUP):
