@@ -304,22 +304,30 @@ __global__ void glu_bias_kernel(const T* __restrict__ src, long long ld, int gat
     }
 }
 
-// the same with eight consecutive bf16 columns per thread (16-byte accesses)
+// the same with eight consecutive bf16 columns per thread (16-byte accesses, biases as two float4 each)
 __global__ void glu_bias_vec_kernel(const bf16* __restrict__ src, long long ld, int gate_off, int up_off,
                                     const float* __restrict__ gb, const float* __restrict__ ub, bf16* __restrict__ out,
                                     long long M, int F8, float limit, float alpha, float up_shift) {
-    const long long total = M * F8;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-        const long long m = i / F8;
-        const int f = (int)(i - m * F8) * 8;
+    const int f = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (f >= F8 * 8) return;
+    float bg[8], bu[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) bg[j] = bu[j] = 0.f;
+    if (gb != nullptr) {
+        *reinterpret_cast<float4*>(bg) = *reinterpret_cast<const float4*>(gb + f);
+        *reinterpret_cast<float4*>(bg + 4) = *reinterpret_cast<const float4*>(gb + f + 4);
+    }
+    if (ub != nullptr) {
+        *reinterpret_cast<float4*>(bu) = *reinterpret_cast<const float4*>(ub + f);
+        *reinterpret_cast<float4*>(bu + 4) = *reinterpret_cast<const float4*>(ub + f + 4);
+    }
+    for (long long m = blockIdx.y; m < M; m += gridDim.y) {
         float g[8], u[8], o[8];
         unpack8(*reinterpret_cast<const bf16x8*>(src + m * ld + gate_off + f), g);
         unpack8(*reinterpret_cast<const bf16x8*>(src + m * ld + up_off + f), u);
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-            o[j] = glu_act(g[j] + (gb != nullptr ? gb[f + j] : 0.f), u[j] + (ub != nullptr ? ub[f + j] : 0.f), limit, alpha,
-                           up_shift);
-        *reinterpret_cast<bf16x8*>(out + (m * F8) * 8 + f) = pack8(o);
+        for (int j = 0; j < 8; ++j) o[j] = glu_act(g[j] + bg[j], u[j] + bu[j], limit, alpha, up_shift);
+        *reinterpret_cast<bf16x8*>(out + m * F8 * 8 + f) = pack8(o);
     }
 }
 
@@ -462,12 +470,12 @@ NXD_API int nxd_glu_bias(int dtype, const void* src, long long ld, int gate_off,
     const long long cap = (long long)nxd_num_sms() * 16;
     if (blocks > cap) blocks = cap;
     if (dtype == 0 && F % 8 == 0 && ld % 8 == 0 && gate_off % 8 == 0 && up_off % 8 == 0 && ((uintptr_t)src % 16) == 0 &&
-        ((uintptr_t)out % 16) == 0) {
-        long long vb = (M * (F / 8) + 255) / 256;
-        if (vb > cap) vb = cap;
-        glu_bias_vec_kernel<<<(unsigned)vb, 256, 0, (cudaStream_t)stream>>>((const bf16*)src, ld, gate_off, up_off, gate_bias,
-                                                                            up_bias, (bf16*)out, M, F / 8, limit, alpha,
-                                                                            up_shift);
+        ((uintptr_t)out % 16) == 0 && ((uintptr_t)gate_bias % 16) == 0 && ((uintptr_t)up_bias % 16) == 0) {
+        const int F8 = F / 8, threads = F8 >= 256 ? 256 : ((F8 + 31) / 32) * 32;
+        const long long rows_cap = (long long)nxd_num_sms() * 32;         // rows beyond that are walked by the same CTAs
+        dim3 grid((F8 + threads - 1) / threads, (unsigned)(M < rows_cap ? M : rows_cap));
+        glu_bias_vec_kernel<<<grid, threads, 0, (cudaStream_t)stream>>>((const bf16*)src, ld, gate_off, up_off, gate_bias,
+                                                                        up_bias, (bf16*)out, M, F8, limit, alpha, up_shift);
         NXD_LAUNCH_CHECK();
         return 0;
     }

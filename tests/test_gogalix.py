@@ -229,7 +229,7 @@ def maps_oracle(q, k, v, pos_q, scale, window):
 
 @case
 @pytest.mark.parametrize("paged", [False, True], ids=["contiguous", "paged"])
-@pytest.mark.parametrize("D,Dv,window", [(8, 12, 9), (32, 32, 33), (64, 64, 16), (10, 3, None)])
+@pytest.mark.parametrize("D,Dv,window", [(8, 12, 9), (32, 32, 33), (64, 64, 16), (10, 3, None), (48, 96, 20), (32, 64, 7)])
 def test_two_maps_over_shared_values_and_the_window_edge(dev, dt, paged, D, Dv, window):
     """Map-major query / key heads (2H over 2G) read G value heads; a key that dominates map 1 is planted so that it is
     just inside the window of one query and just outside the next one's, in a prompt portion and in decoding."""
