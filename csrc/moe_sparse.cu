@@ -6,6 +6,7 @@
 //                 weight = s * out_scale (not renormalised);  optional second output sigmoid(<w_sg, h>) per token.
 //                 renormalise: the `top` largest LOGITS are taken and the weights are the softmax over the chosen
 //                 logits only (times out_scale)
+//                 sigmoid scores (mode 2): s = sigmoid(z) per expert instead of the softmax, otherwise as the first form
 //   activation    g = min(gate, limit), u = clamp(up, -limit, limit);  a = g * sigmoid(alpha * g) * (u + up_shift)
 //                 (limit = +inf, alpha = 1, up_shift = 0: plain silu(gate) * up)
 //   expert index >= E means an identity expert: its output is the token's input itself
@@ -29,10 +30,13 @@ __device__ __forceinline__ void ld2(const bf16* p, float& a, float& b) {
     b = v.y;
 }
 
-__device__ __forceinline__ float glu_act(float g, float u, float limit, float alpha, float up_shift) {
+// kind 0: g * sigmoid(alpha g); kind 1: the tanh form of gelu, 0.5 g (1 + tanh(c (g + 0.044715 g^3))) with c = sqrt(2 / pi),
+// written through 0.5 (1 + tanh(a)) = sigmoid(2 a)
+__device__ __forceinline__ float glu_act(float g, float u, float limit, float alpha, float up_shift, int kind = 0) {
     g = fminf(g, limit);
     u = fminf(fmaxf(u, -limit), limit);
-    return g / (1.f + expf(-alpha * g)) * (u + up_shift);
+    const float a = kind == 1 ? 1.5957691216057308f * (g + 0.044715f * g * g * g) : alpha * g;
+    return g / (1.f + expf(-a)) * (u + up_shift);
 }
 
 // ---- router ---------------------------------------------------------------------------------------------------------
@@ -43,8 +47,9 @@ __global__ void __launch_bounds__(RT_WARPS * 32)
 moe_router_kernel(const T* __restrict__ h, const float* __restrict__ wr, const float* __restrict__ corr,
                   const float* __restrict__ wsg, int* __restrict__ idx, float* __restrict__ wts,
                   float* __restrict__ sgate, long long N, int W, int R, int top, float out_scale,
-                  const float* __restrict__ zbias, int renorm) {
+                  const float* __restrict__ zbias, int mode) {
     extern __shared__ float smem[];
+    const bool renorm = mode == 1;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     float* ps = smem + (long long)warp * 2 * R;     // probabilities
     float* cs = ps + R;                             // choice scores
@@ -76,6 +81,12 @@ moe_router_kernel(const T* __restrict__ h, const float* __restrict__ wr, const f
     __syncwarp();
     if (renorm) {                // the choice is made on the logits themselves
         for (int r = lane; r < R; r += 32) cs[r] = ps[r];
+    } else if (mode == 2) {      // independent sigmoid scores
+        for (int r = lane; r < R; r += 32) {
+            const float p = 1.f / (1.f + expf(-ps[r]));
+            ps[r] = p;
+            cs[r] = p + (corr != nullptr ? corr[r] : 0.f);
+        }
     } else {
         float mx = -INFINITY;
         for (int r = lane; r < R; r += 32) mx = fmaxf(mx, ps[r]);
@@ -139,7 +150,7 @@ template <typename T, bool VEC>
 __global__ void __launch_bounds__(GV_WARPS * 32)
 moe_gate_up_act_kernel(const T* __restrict__ h, const T* __restrict__ wgu, const int* __restrict__ idx,
                        T* __restrict__ act, int pairs_per_token, int W, int F, int E, float limit, float alpha,
-                       float up_shift) {
+                       float up_shift, const float* __restrict__ in_scale) {
     extern __shared__ float smem[];
     constexpr int PER = VEC ? 2 : 1, COLS = 32 * PER;
     float* hs = smem;                                  // [W]
@@ -149,7 +160,8 @@ moe_gate_up_act_kernel(const T* __restrict__ h, const T* __restrict__ wgu, const
     if (e < 0 || e >= E) return;                       // identity expert: no intermediate
     const long long t = p / pairs_per_token;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    for (int c = threadIdx.x; c < W; c += GV_WARPS * 32) hs[c] = ldf(h + t * W + c);
+    const float xs = in_scale != nullptr ? in_scale[p] : 1.f;       // the pair's weight applied to the expert's INPUT
+    for (int c = threadIdx.x; c < W; c += GV_WARPS * 32) hs[c] = ldf(h + t * W + c) * xs;
     __syncthreads();
     const int f0 = blockIdx.y * COLS + lane * PER;
     const int per = (W + GV_WARPS - 1) / GV_WARPS;
@@ -293,21 +305,21 @@ __global__ void clamped_glu_kernel(const T* __restrict__ gu, T* __restrict__ out
 template <typename T>
 __global__ void glu_bias_kernel(const T* __restrict__ src, long long ld, int gate_off, int up_off,
                                 const float* __restrict__ gb, const float* __restrict__ ub, T* __restrict__ out, long long M,
-                                int F, float limit, float alpha, float up_shift) {
+                                int F, float limit, float alpha, float up_shift, int kind) {
     const long long total = M * F;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const long long m = i / F;
         const int f = (int)(i - m * F);
         const float g = ldf(src + m * ld + gate_off + f) + (gb != nullptr ? gb[f] : 0.f);
         const float u = ldf(src + m * ld + up_off + f) + (ub != nullptr ? ub[f] : 0.f);
-        stf(out + i, glu_act(g, u, limit, alpha, up_shift));
+        stf(out + i, glu_act(g, u, limit, alpha, up_shift, kind));
     }
 }
 
 // the same with eight consecutive bf16 columns per thread (16-byte accesses, biases as two float4 each)
 __global__ void glu_bias_vec_kernel(const bf16* __restrict__ src, long long ld, int gate_off, int up_off,
                                     const float* __restrict__ gb, const float* __restrict__ ub, bf16* __restrict__ out,
-                                    long long M, int F8, float limit, float alpha, float up_shift) {
+                                    long long M, int F8, float limit, float alpha, float up_shift, int kind) {
     const int f = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
     if (f >= F8 * 8) return;
     float bg[8], bu[8];
@@ -326,7 +338,7 @@ __global__ void glu_bias_vec_kernel(const bf16* __restrict__ src, long long ld, 
         unpack8(*reinterpret_cast<const bf16x8*>(src + m * ld + gate_off + f), g);
         unpack8(*reinterpret_cast<const bf16x8*>(src + m * ld + up_off + f), u);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = glu_act(g[j] + bg[j], u[j] + bu[j], limit, alpha, up_shift);
+        for (int j = 0; j < 8; ++j) o[j] = glu_act(g[j] + bg[j], u[j] + bu[j], limit, alpha, up_shift, kind);
         *reinterpret_cast<bf16x8*>(out + m * F8 * 8 + f) = pack8(o);
     }
 }
@@ -353,10 +365,11 @@ __global__ void moe_gather_combine_kernel(const T* __restrict__ ys, const int* _
 }  // namespace
 
 // dtype: 0 bf16, 1 fp32 (activations and expert weights).  R = router outputs (experts + identity experts).
-// zbias [R] fp32 or NULL: added to the logits; renorm != 0: choice on the logits, weights = softmax over the chosen ones.
+// zbias [R] fp32 or NULL: added to the logits; mode 0: softmax scores; 1: choice on the logits, weights = softmax over the
+// chosen ones; 2: sigmoid scores.
 NXD_API int nxd_moe_router(int dtype, const void* h, const float* wr, const float* corr, const float* wsg, int* idx,
                            float* wts, float* sgate, long long N, int W, int R, int top, float out_scale,
-                           const float* zbias, int renorm, void* stream) {
+                           const float* zbias, int mode, void* stream) {
     if (N == 0) return 0;
     NXD_REQUIRE(top >= 1 && top <= R, "router: top %d of %d", top, R);
     const size_t smem = (size_t)RT_WARPS * 2 * R * sizeof(float);
@@ -365,20 +378,21 @@ NXD_API int nxd_moe_router(int dtype, const void* h, const float* wr, const floa
     if (dtype == 0)
         moe_router_kernel<bf16><<<blocks, RT_WARPS * 32, smem, (cudaStream_t)stream>>>((const bf16*)h, wr, corr, wsg, idx,
                                                                                       wts, sgate, N, W, R, top, out_scale,
-                                                                                      zbias, renorm);
+                                                                                      zbias, mode);
     else
         moe_router_kernel<float><<<blocks, RT_WARPS * 32, smem, (cudaStream_t)stream>>>((const float*)h, wr, corr, wsg,
                                                                                        idx, wts, sgate, N, W, R, top,
-                                                                                       out_scale, zbias, renorm);
+                                                                                       out_scale, zbias, mode);
     NXD_LAUNCH_CHECK();
     return 0;
 }
 
 // act[p, :] = activation(h[p / pairs_per_token] @ wgu[idx[p]]) for P pairs; idx NULL = expert 0 for every pair (a dense
-// gated MLP); pairs whose index is outside [0, E) are identity experts and are skipped.
+// gated MLP); pairs whose index is outside [0, E) are identity experts and are skipped.  in_scale [P] fp32 or NULL: the
+// pair's input row is multiplied by it (routing weight on the expert's input).
 NXD_API int nxd_moe_gate_up_act(int dtype, const void* h, const void* wgu, const int* idx, void* act, long long P,
                                 int pairs_per_token, int W, int F, int E, float limit, float alpha, float up_shift,
-                                void* stream) {
+                                const float* in_scale, void* stream) {
     if (P == 0) return 0;
     NXD_REQUIRE(P < (1ll << 31), "gate/up: %lld pairs", P);
     const bool vec = (F % 2) == 0;
@@ -393,7 +407,7 @@ NXD_API int nxd_moe_gate_up_act(int dtype, const void* h, const void* wgu, const
         if (smem > 48 * 1024)                                                                                         \
             NXD_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));       \
         kern<<<grid, GV_WARPS * 32, smem, st>>>((const T*)h, (const T*)wgu, idx, (T*)act, pairs_per_token, W, F, E,   \
-                                                limit, alpha, up_shift);                                              \
+                                                limit, alpha, up_shift, in_scale);                                    \
     } while (0)
     if (dtype == 0) {
         if (vec) NXD_GU(bf16, true); else NXD_GU(bf16, false);
@@ -464,7 +478,7 @@ NXD_API int nxd_moe_gather_combine(int dtype, const void* ys, const int* slot, c
 
 NXD_API int nxd_glu_bias(int dtype, const void* src, long long ld, int gate_off, int up_off, const float* gate_bias,
                          const float* up_bias, void* out, long long M, int F, float limit, float alpha, float up_shift,
-                         void* stream) {
+                         int act_kind, void* stream) {
     if (M * F == 0) return 0;
     long long blocks = (M * F + 255) / 256;
     const long long cap = (long long)nxd_num_sms() * 16;
@@ -475,18 +489,19 @@ NXD_API int nxd_glu_bias(int dtype, const void* src, long long ld, int gate_off,
         const long long rows_cap = (long long)nxd_num_sms() * 32;         // rows beyond that are walked by the same CTAs
         dim3 grid((F8 + threads - 1) / threads, (unsigned)(M < rows_cap ? M : rows_cap));
         glu_bias_vec_kernel<<<grid, threads, 0, (cudaStream_t)stream>>>((const bf16*)src, ld, gate_off, up_off, gate_bias,
-                                                                        up_bias, (bf16*)out, M, F8, limit, alpha, up_shift);
+                                                                        up_bias, (bf16*)out, M, F8, limit, alpha, up_shift,
+                                                                        act_kind);
         NXD_LAUNCH_CHECK();
         return 0;
     }
     if (dtype == 0)
         glu_bias_kernel<bf16><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((const bf16*)src, ld, gate_off, up_off,
                                                                                  gate_bias, up_bias, (bf16*)out, M, F, limit,
-                                                                                 alpha, up_shift);
+                                                                                 alpha, up_shift, act_kind);
     else
         glu_bias_kernel<float><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((const float*)src, ld, gate_off, up_off,
                                                                                   gate_bias, up_bias, (float*)out, M, F,
-                                                                                  limit, alpha, up_shift);
+                                                                                  limit, alpha, up_shift, act_kind);
     NXD_LAUNCH_CHECK();
     return 0;
 }

@@ -54,7 +54,8 @@ __global__ void qk_norm_cache_write_kernel(const T* __restrict__ qkv, long long 
                                            int Dv, int has_kv, int normalize, float eps, int max_pos, int writeback,
                                            const float* __restrict__ q_weight, const float* __restrict__ k_weight,
                                            const float* __restrict__ rope_cos, const float* __restrict__ rope_sin,
-                                           int rope_dims, int value_from_key, int Gv) {
+                                           int rope_dims, int value_from_key, int Gv, int rope_halves,
+                                           int whole_norm) {
     const int lane = threadIdx.x & 31;
     const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (unit >= units) return;
@@ -89,33 +90,40 @@ __global__ void qk_norm_cache_write_kernel(const T* __restrict__ qkv, long long 
     }
     float r = 1.f;
     if (hd < H + G && normalize) {
+        // whole_norm: the statistic runs over all heads of the projection (queries: H * D values, keys: G * D) and the
+        // weight has that size; else over the head alone, with a weight of D values shared by the heads
+        const T* stat = whole_norm ? (hd < H ? qkv + n * ld : qkv + n * ld + (long long)H * D) : src;
+        const int cnt = whole_norm ? (hd < H ? H : G) * D : dim;
         float ss = 0.f;
-        for (int i = lane; i < dim; i += 32) {
-            const float v = ldf(src + i);
+        for (int i = lane; i < cnt; i += 32) {
+            const float v = ldf(stat + i);
             ss += v * v;
         }
         ss = warp_sum(ss);
-        r = 1.f / sqrtf(ss / (float)dim + eps);
+        r = 1.f / sqrtf(ss / (float)cnt + eps);
     }
     // writeback: the normalised keys also replace the raw ones in the projection buffer, so that a kernel that reads
     // q / k / v as strided views of that buffer (prefill from position 0) sees what the cache holds
     T* back = (writeback && hd >= H && hd < H + G) ? const_cast<T*>(src) : nullptr;
     const float* wgt = hd < H ? q_weight : (hd < H + G ? k_weight : nullptr);
+    if (wgt != nullptr && whole_norm) wgt += (long long)(hd < H ? hd : hd - H) * D;
     const int rot = (hd < H + G && rope_cos != nullptr) ? rope_dims : 0;
-    // rotated part: the pair (2i, 2i + 1) turns by the angle of (position, i); cos / sin come from a table [pos][i]
+    // rotated part: pair i turns by the angle of (position, i); cos / sin come from a table [pos][i].  The pair is the
+    // dimensions (2i, 2i + 1), or with rope_halves (i, i + rot / 2)
     if (rot > 0) {
         const long long pos = (long long)q_start[b] + t;
         const float* cs = rope_cos + pos * (rope_dims / 2);
         const float* sn = rope_sin + pos * (rope_dims / 2);
         for (int i = lane; i < rot / 2; i += 32) {
-            float u = ldf(src + 2 * i) * r, v = ldf(src + 2 * i + 1) * r;
+            const int iu = rope_halves ? i : 2 * i, iv = rope_halves ? i + rot / 2 : 2 * i + 1;
+            float u = ldf(src + iu) * r, v = ldf(src + iv) * r;
             if (wgt != nullptr) {
-                u *= wgt[2 * i];
-                v *= wgt[2 * i + 1];
+                u *= wgt[iu];
+                v *= wgt[iv];
             }
             const float c = cs[i], s = sn[i];
-            stf(dst + 2 * i, u * c - v * s);
-            stf(dst + 2 * i + 1, v * c + u * s);
+            stf(dst + iu, u * c - v * s);
+            stf(dst + iv, v * c + u * s);
         }
     }
     for (int i = rot + lane; i < dim; i += 32) {
@@ -921,7 +929,9 @@ int launch_decode(const void* q, const void* ck, const void* cv, CacheAddr ka, C
 // new token of every row; n_new [B] or NULL: how many of the Tn rows are real (the others are padding and write
 // nothing); seq_ids [B] or NULL: cache line of every row.  max_pos: rows of a cache line.
 // q_weight / k_weight [D] fp32 or NULL: weight of the per-head norm.  rope_cos / rope_sin [positions, rope_dims / 2]
-// fp32 or NULL: queries and keys (after the norm) turn pairwise, (2i, 2i + 1), on their first rope_dims dimensions.
+// fp32 or NULL: queries and keys (after the norm) turn pairwise, (2i, 2i + 1), on their first rope_dims dimensions
+// (rope_halves: the pairs are (i, i + rope_dims / 2)).  whole_norm: the norm's statistic runs over all query heads (all
+// key heads) of a row at once and q_weight / k_weight hold H * D / G * D values.
 // value_from_key: the row has no value columns, the cached value is the raw key projection (taken ahead of the norm and the rotation).
 NXD_API int nxd_qk_prep_cache_write(int dtype, const void* qkv, long long ld, void* q_out, void* cache_k, void* cache_v,
                                     long long k_stride_line, long long k_stride_head, long long v_stride_line,
@@ -930,7 +940,7 @@ NXD_API int nxd_qk_prep_cache_write(int dtype, const void* qkv, long long ld, vo
                                     int D, int Dv, int has_kv, int normalize, float eps, int max_pos, int writeback,
                                     const float* q_weight, const float* k_weight, const float* rope_cos,
                                     const float* rope_sin, int rope_dims, int value_from_key, int value_heads,
-                                    void* stream) {
+                                    int rope_halves, int whole_norm, void* stream) {
     const int Gv = value_heads > 0 ? value_heads : G;
     const long long units = (long long)B * Tn * (H + (has_kv ? G + Gv : 0));
     if (units == 0) return 0;
@@ -946,12 +956,12 @@ NXD_API int nxd_qk_prep_cache_write(int dtype, const void* qkv, long long ld, vo
         qk_norm_cache_write_kernel<bf16><<<blocks, wpb * 32, 0, (cudaStream_t)stream>>>(
             (const bf16*)qkv, ld, (bf16*)q_out, (bf16*)cache_k, (bf16*)cache_v, ka, va, q_start, n_new, seq_ids, units, Tn,
             H, G, D, Dv, has_kv, normalize, eps, max_pos, writeback, q_weight, k_weight, rope_cos, rope_sin, rope_dims,
-            value_from_key, Gv);
+            value_from_key, Gv, rope_halves, whole_norm);
     else
         qk_norm_cache_write_kernel<float><<<blocks, wpb * 32, 0, (cudaStream_t)stream>>>(
             (const float*)qkv, ld, (float*)q_out, (float*)cache_k, (float*)cache_v, ka, va, q_start, n_new, seq_ids, units,
             Tn, H, G, D, Dv, has_kv, normalize, eps, max_pos, writeback, q_weight, k_weight, rope_cos, rope_sin, rope_dims,
-            value_from_key, Gv);
+            value_from_key, Gv, rope_halves, whole_norm);
     NXD_LAUNCH_CHECK();
     return 0;
 }
@@ -965,7 +975,7 @@ NXD_API int nxd_qk_norm_cache_write(int dtype, const void* qkv, long long ld, vo
     return nxd_qk_prep_cache_write(dtype, qkv, ld, q_out, cache_k, cache_v, k_stride_line, k_stride_head, v_stride_line,
                                    v_stride_head, block_table, page_size, table_cols, q_start, n_new, seq_ids, B, Tn, H, G,
                                    D, Dv, has_kv, normalize, eps, max_pos, writeback, nullptr, nullptr, nullptr, nullptr, 0,
-                                   0, 0, stream);
+                                   0, 0, 0, 0, stream);
 }
 
 // q [B, Tn, H, D] -> out [B, Tn, H, Dv]; the keys and values of positions [0, q_start[b] + n_new[b]) are read from the

@@ -304,14 +304,17 @@ int nxd_window_attn_decode(int dtype, const void* q, const void* cache_k, const 
 /* The same kernels with a chunk mask (chunk > 0: floor(i / chunk) == floor(j / chunk) as well), a per-head sink logit in
  * the softmax denominator (sinks [H] fp32 or NULL) and explicit cache-row pitches (k_row, v_row, in elements: v_row ==
  * k_row when the values are columns of the key rows).  nxd_qk_prep_cache_write adds norm weights (fp32 [D] or NULL),
- * pairwise rotation from cos / sin tables [positions, rope_dims / 2] and value_from_key (cached value = raw key). */
+ * pairwise rotation from cos / sin tables [positions, rope_dims / 2] (pairs (2i, 2i + 1), or with rope_halves
+ * (i, i + rope_dims / 2)), value_from_key (cached value = raw key) and whole_norm (the norm's statistic over all query /
+ * all key heads of a row at once, weights of H * D / G * D values). */
 int nxd_qk_prep_cache_write(int dtype, const void* qkv, long long ld, void* q_out, void* cache_k, void* cache_v,
                             long long k_stride_line, long long k_stride_head, long long v_stride_line,
                             long long v_stride_head, const int* block_table, int page_size, int table_cols,
                             const int* q_start, const int* n_new, const int* seq_ids, int B, int Tn, int H, int G, int D,
                             int Dv, int has_kv, int normalize, float eps, int max_pos, int writeback,
                             const float* q_weight, const float* k_weight, const float* rope_cos, const float* rope_sin,
-                            int rope_dims, int value_from_key, int value_heads, void* stream);
+                            int rope_dims, int value_from_key, int value_heads, int rope_halves, int whole_norm,
+                            void* stream);
 /* value_heads (0 = as many as key heads): head g of the value cache serves the key heads g, g + value_heads, ...
  * (several attention maps over the same values); the projection row then holds value_heads value heads. */
 int nxd_masked_attn_prefill(int dtype, const void* q, const void* cache_k, const void* cache_v, long long k_stride_line,
@@ -385,18 +388,22 @@ int nxd_delta_scan(const float* qn, const float* kn, const float* vn, float* apr
                    float* bpre, long long ld_b, int b_off, const float* a_log, const float* dt_bias, float* S,
                    float* out, const int* q_start, const int* n_new, const int* seq_ids, int B, int Tn, int H, int G, int D,
                    int Dv, int per_channel, void* stream);
-/* gate and up columns of a wider row (+ fp32 biases or NULL) -> gated activation as in nxd_clamped_glu, out [rows, F] */
+/* gate and up columns of a wider row (+ fp32 biases or NULL) -> gated activation as in nxd_clamped_glu, out [rows, F];
+ * act_kind 1: the gate goes through the tanh form of gelu instead of g * sigmoid(alpha g) */
 int nxd_glu_bias(int dtype, const void* src, long long ld, int gate_off, int up_off, const float* gate_bias,
                  const float* up_bias, void* out, long long rows, int F, float limit, float alpha, float up_shift,
-                 void* stream);
+                 int act_kind, void* stream);
 /* router: s = softmax(wr h + zbias); the `top` largest (s + corr) are chosen, weight = s * out_scale; sgate =
- * sigmoid(<wsg, h>).  renorm != 0: the `top` largest logits are chosen, weight = softmax over the chosen logits */
+ * sigmoid(<wsg, h>).  mode 1: the `top` largest logits are chosen, weight = softmax over the chosen logits; mode 2:
+ * s = sigmoid of every logit instead of the softmax */
 int nxd_moe_router(int dtype, const void* h, const float* wr, const float* corr, const float* wsg, int* idx, float* wts,
-                   float* sgate, long long N, int W, int R, int top, float out_scale, const float* zbias, int renorm,
+                   float* sgate, long long N, int W, int R, int top, float out_scale, const float* zbias, int mode,
                    void* stream);
-/* expert weights [E, in, out]; an index outside [0, E) is an identity expert */
+/* expert weights [E, in, out]; an index outside [0, E) is an identity expert; in_scale [P] fp32 or NULL multiplies the
+ * pair's input row */
 int nxd_moe_gate_up_act(int dtype, const void* h, const void* wgu, const int* idx, void* act, long long P,
-                        int pairs_per_token, int W, int F, int E, float limit, float alpha, float up_shift, void* stream);
+                        int pairs_per_token, int W, int F, int E, float limit, float alpha, float up_shift,
+                        const float* in_scale, void* stream);
 int nxd_moe_down_combine(int dtype, const void* act, const void* wd, const int* idx, const float* wts, const void* h,
                          const void* act_s, const void* wds, const float* sgate, float* y, long long N, int top, int W,
                          int F, int Fs, int E, void* stream);
@@ -405,6 +412,27 @@ int nxd_clamped_glu(int dtype, const void* gate_up, void* out, long long M, int 
 int nxd_moe_gather_combine(int dtype, const void* ys, const int* slot, const int* idx, const float* wts, const void* h,
                            const void* shared_out, const float* sgate, float* y, long long N, int top, int W, int E,
                            void* stream);
+
+/* Retention (csrc/retention.cu): S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t on the fp32 state [lines, H, D, Dv] of
+ * cache line seq_ids[b] (or b; zero state where q_start[b] == 0).  proj [B * Tn, ld] holds q / k / v head-major at the
+ * column offsets (dtype 0 bf16, 1 fp32); q and k turn on their first rot dimensions by cos / sin tables [max_pos, rot / 2]
+ * (NULL: no rotation; halves: pairs (i, i + rot / 2), else (2i, 2i + 1)), k is multiplied by kscale afterwards.
+ * out [B * Tn, H, Dv] fp32; tokens t >= n_new[b] are padding.  The chunk-wise form (chunks of 64 tokens) needs fp32
+ * scratch U [B, H, ceil(Tn / 64), D, Dv] and qrot [B * Tn, H, D]. */
+int nxd_retention_scan(int dtype, const void* proj, long long ld, int q_off, int k_off, int v_off, const float* decay,
+                       float* state, float* out, const int* q_start, const int* n_new, const int* seq_ids, int B, int Tn,
+                       int H, int D, int Dv, float kscale, const float* rope_cos, const float* rope_sin, int rot,
+                       int halves, int max_pos, void* stream);
+int nxd_retention_chunkwise(int dtype, const void* proj, long long ld, int q_off, int k_off, int v_off, const float* decay,
+                            float* state, float* out, float* U, float* qrot, const int* q_start, const int* n_new,
+                            const int* seq_ids, int B, int Tn, int H, int D, int Dv, float kscale, const float* rope_cos,
+                            const float* rope_sin, int rot, int halves, int max_pos, void* stream);
+/* Hyper-connections (csrc/hyper_connection.cu): X [N, S, W] fp32 streams.  ya != NULL: x_t <- sum_s mix[s][t] x_s +
+ * outw[t] * y with y = ya, or (yb != NULL) 0.5 * (rmsnorm(ya) * wa + rmsnorm(yb) * wb).  inw != NULL: h [N, W] = RMS norm
+ * (weight wn) of sum_s inw[s] x_s, of the streams as the write left them.  y_dtype / h_dtype: 0 bf16, 1 fp32. */
+int nxd_hc_step(int y_dtype, int h_dtype, float* X, const void* ya, const void* yb, const float* wa, const float* wb,
+                const float* mix, const float* outw, const float* inw, const float* wn, void* h, long long N, int S, int W,
+                float eps, void* stream);
 
 #ifdef __cplusplus
 }

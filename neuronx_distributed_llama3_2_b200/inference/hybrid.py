@@ -1,5 +1,5 @@
 """Hybrid families (recurrent mixers next to attention over the cache) over the framework's step function: Rasodra and,
-further down, Gogalix.
+further down, Gogalix and Vufasun.
 
 Rasodra over the framework's step function: chunked attention, latent attention and the recurrent matrix memory on
 one KV cache / state manager.
@@ -30,13 +30,16 @@ import torch
 
 from ..models.gogalix import UNIT_NORM_EPS, GogalixConfig, GogalixForCausalLM
 from ..models.rasodra import RasodraConfig, RasodraForCausalLM
+from ..models.vufasun import VufasunConfig, VufasunForCausalLM
 from ..ops import activation as act_ops
 from ..ops import attention as attn_ops
 from ..ops import delta_rule as delta_ops
+from ..ops import hyper_connection as hc_ops
 from ..ops import latent_attention as la_ops
 from ..ops import mlstm as mlstm_ops
 from ..ops import moe_sparse as moe_ops
 from ..ops import norm as norm_ops
+from ..ops import retention as ret_ops
 from ..ops import rope as rope_ops
 from ..ops import window_attention as wa_ops
 from ..ops.linear import gemm_nt
@@ -397,6 +400,167 @@ class GogalixInferenceModel(KVCacheInferenceMixin, GogalixForCausalLM):
         if self.layer_probe is not None:
             self.layer_probe(i, x.view(B, T, W))
         return x.view(B, T, W), (h_next.view(B, T, W) if h_next is not None else None)
+
+    def forward_speculation(self, *a, **kw):
+        raise NotImplementedError("the speculation verify graph is not wired for this family")
+
+
+class VufasunInferenceModel(KVCacheInferenceMixin, VufasunForCausalLM):
+    """Vufasun over the KV cache / state manager.  The step function (padding, cache lines through ``seq_ids``, indexed
+    logits, sampler, ``generate``), the schedulers and the runners are the mixin's; this class says what a layer does:
+
+      * ``hidden`` is the fp32 streams ``[B, T, streams * W]`` (stream-major per token), ``residual`` carries the normed
+        weighted sum that the sublayer about to run reads, in the activation dtype: the write of a sublayer's output into
+        the streams and the read of the next sublayer are one kernel (``ops.hyper_connection.hc_step``);
+      * ONE matrix product of the mixer's input gives all its projections (``layer.in_proj``, parts at
+        ``layer.columns``); the kernels read their part in place;
+      * softmax attention: whole-projection norm (left branch of a parallel layer) + "rotate half" rotation + cache write
+        in one kernel, then attention over the cache with the sink logit in the denominator (``attention`` layers);
+      * retention: rotation, key scale and the recurrence on the line's fp32 state in one kernel (token by token, or in
+        chunks of 64 tokens for long steps), then unit RMS per head * ``silu`` gate;
+      * a parallel layer hands both branch outputs to the stream kernel, which norms and averages them;
+      * a looped layer appears once per pass in the run list: same modules, cache / state of the run's own index.
+    A step may start at any position: attention reads earlier keys from the cache, the recurrence continues from the
+    line's state."""
+
+    supports_prefill_at_offset = True
+    CHUNKWISE_MIN_TOKENS = 64            # shorter steps walk the recurrence token by token
+
+    def __init__(self, config: VufasunConfig, inference_config: Optional[InferenceConfig] = None, device=None):
+        VufasunForCausalLM.__init__(self, config, device=device)
+        self._init_inference(inference_config)
+        self._sequence = self.layer_sequence()
+        self._rope_cache: Dict[tuple, Tuple[torch.Tensor, torch.Tensor]] = {}
+        self._unit_in: Optional[torch.Tensor] = None
+        self.layer_probe = None            # callable(i, x) after every layer run (debugging / layer-by-layer checks)
+
+    def _decoder_layers(self):
+        return self._sequence
+
+    def _embedding(self):
+        return self.embed_tokens
+
+    def _final_norm(self):
+        return self.norm
+
+    def init_kv_cache(self, device=None, dtype=None) -> KVCache:
+        ic, cfg = self.inference_config, self.config
+        device = device or next(self.parameters()).device
+        specs, states = [], {}
+        for run, li in enumerate(cfg.layer_runs()):           # one cache / state entry per layer RUN
+            L = cfg.layers[li]
+            a = L.mixer if L.type == "attention" else L.mixer.left
+            specs.append((a.kv_heads, a.dim, a.vdim))
+            if L.type == "parallel":
+                r = L.mixer.right
+                states[run] = {"S": (r.heads, r.dim, r.vdim)}
+        self.kv_cache = KVCache(len(specs), ic.max_batch_size, 0, ic.seq_len, 0, dtype=dtype or cfg.torch_dtype,
+                                device=device, paged=ic.paged_kv, page_size=ic.page_size,
+                                num_pages=ic.num_kv_pages if ic.paged_kv else None, layer_specs=specs, state_specs=states)
+        return self.kv_cache
+
+    def _rotary_tables(self, rot, device) -> Optional[Tuple[torch.Tensor, torch.Tensor]]:
+        if rot is None:
+            return None
+        key = (rot.dims, rot.base, rot.scaling)
+        t = self._rope_cache.get(key)
+        if t is None or t[0].device != device or t[0].shape[0] < self.kv_cache.seq_len:
+            t = rope_ops.build_interleaved_rope_cache(self.kv_cache.seq_len, rot.dims, rot.base, device=device,
+                                                      scaling=rot.scaling)
+            self._rope_cache[key] = t
+        return t
+
+    def _embed(self, input_ids: torch.Tensor) -> torch.Tensor:
+        x = super()._embed(input_ids).float()                 # every stream starts as the embedding, in fp32
+        B, T, W = x.shape
+        S = self.config.streams
+        return x.unsqueeze(2).expand(B, T, S, W).reshape(B, T, S * W)
+
+    def _add_norm(self, norm, hidden: torch.Tensor, residual: Optional[torch.Tensor]):
+        """Only the model's final norm comes through here: RMS norm of the plain sum of the streams."""
+        S, W = self.config.streams, self.config.hidden_size
+        if self._unit_in is None or self._unit_in.device != hidden.device:
+            self._unit_in = torch.ones(S, dtype=torch.float32, device=hidden.device)
+        x = hidden.reshape(-1, S, W)
+        h = hc_ops.hc_step(x if x.is_contiguous() else x.contiguous(), in_w=self._unit_in, norm_w=norm,
+                           eps=self.config.rms_norm_eps, out_dtype=self.config.torch_dtype)
+        return h.reshape(hidden.shape[:-1] + (W,)), None
+
+    def _paged(self) -> dict:
+        kc = self.kv_cache
+        return dict(block_table=kc.block_table, page_size=kc.page_size) if kc.paged else {}
+
+    # -- mixers: columns of big [B, T, n_out] = the fused projection of the normed input -> [N, W] ------------------------
+    def _softmax_attention(self, run, mixer, big, at, B, T, q_start, n_new, seq_ids):
+        m, cfg = mixer.cfg, self.config
+        ck, cv = self.kv_cache.layer(run)
+        paged = self._paged()
+        qkv = big[..., at: at + m.columns]
+        q = wa_ops.qk_norm_cache_write(qkv, ck, cv, q_start, m.heads, m.kv_heads, m.dim, m.vdim, cfg.rms_norm_eps,
+                                       n_new=n_new, seq_ids=seq_ids, normalize=m.whole_norm, q_weight=mixer.q_norm,
+                                       k_weight=mixer.k_norm, rope=self._rotary_tables(m.rot, big.device),
+                                       rope_layout="halves", whole_norm=m.whole_norm, **paged)
+        if T == 1:
+            o = wa_ops.window_attention_decode(q[:, 0], ck, cv, q_start, m.scale, seq_ids=seq_ids, sinks=mixer.sink,
+                                               **paged)
+        else:
+            o = wa_ops.window_attention_prefill(q, ck, cv, q_start, m.scale, n_new=n_new, seq_ids=seq_ids,
+                                                sinks=mixer.sink, **paged)
+        return gemm_nt(o.reshape(B * T, m.heads * m.vdim), mixer.o_proj.weight)
+
+    def _retention(self, run, mixer, big, at, B, T, q_start, n_new, seq_ids):
+        m, cfg, dt = mixer.cfg, self.config, self.config.torch_dtype
+        H, D, Dv, N = m.heads, m.dim, m.vdim, B * T
+        state = self.kv_cache.state(run)["S"]
+        offsets = (at, at + H * D, at + 2 * H * D)
+        step = ret_ops.retention_chunkwise if T >= self.CHUNKWISE_MIN_TOKENS else ret_ops.retention_scan
+        o = step(big, offsets, mixer.decay, state, q_start, H, D, Dv, D ** -0.5,
+                 rope=self._rotary_tables(m.rot, big.device), rope_layout="halves", n_new=n_new, seq_ids=seq_ids)
+        y = mlstm_ops.head_norm_gate(o.reshape(N, H, Dv), big.view(N, -1), at + 2 * H * D + H * Dv, H, Dv, None,
+                                     cfg.rms_norm_eps, True, dt, gate_act="silu")
+        return gemm_nt(y, mixer.o_proj.weight)
+
+    def _feed_forward(self, layer, h2: torch.Tensor) -> torch.Tensor:
+        if layer.mlp_kind == "moe":
+            return layer.mlp(h2)                                       # fp32 [N, W]
+        mlp = layer.mlp
+        gu = gemm_nt(h2, mlp.gate_up_proj.weight)
+        act = moe_ops.glu_bias(gu, 0, mlp.ff_pad, mlp.ff, act="gelu_tanh")
+        return gemm_nt(act, mlp.down_proj.weight)
+
+    # -- one layer run ------------------------------------------------------------------------------------------------
+    def _layer(self, i: int, layer, hidden, residual, positions, seq_ids, lengths, prefill):
+        cfg, dt, eps = self.config, self.config.torch_dtype, self.config.rms_norm_eps
+        B, T, SW = hidden.shape
+        S, W, N = cfg.streams, cfg.hidden_size, B * T
+        x = (hidden if hidden.is_contiguous() else hidden.contiguous()).view(N, S, W)
+        h = (residual.reshape(N, W) if residual is not None else
+             hc_ops.hc_step(x, in_w=layer.hc1_in, norm_w=layer.norm1, eps=eps, out_dtype=dt))
+        if "q_start" not in self._step_kv:      # one int32 copy of the rows' first positions per step, not per kernel
+            self._step_kv["q_start"] = positions[:, 0].to(torch.int32).contiguous()
+        q_start = self._step_kv["q_start"]
+        n_new = self._step_new_tokens if prefill else None
+        big = gemm_nt(h, layer.in_proj.weight).view(B, T, -1)
+        y2 = branch_w = None
+        if layer.type == "attention":
+            y = self._softmax_attention(i, layer.mixer, big, layer.columns["qkv"][0], B, T, q_start, n_new, seq_ids)
+        else:
+            y = self._softmax_attention(i, layer.mixer.left, big, layer.columns["left"][0], B, T, q_start, n_new, seq_ids)
+            y2 = self._retention(i, layer.mixer.right, big, layer.columns["right"][0], B, T, q_start, n_new, seq_ids)
+            branch_w = (layer.mixer.left_out, layer.mixer.right_out)
+        nxt = self._sequence[i + 1] if i + 1 < len(self._sequence) else None
+        in_next, norm_next = (nxt.hc1_in, nxt.norm1) if nxt is not None else (None, None)
+        if layer.mlp is None:
+            h_next = hc_ops.hc_step(x, y, layer.hc1_mix, layer.hc1_out, in_next, norm_next, eps, dt, y2=y2,
+                                    branch_w=branch_w)
+        else:
+            h2 = hc_ops.hc_step(x, y, layer.hc1_mix, layer.hc1_out, layer.hc2_in, layer.norm2, eps, dt, y2=y2,
+                                branch_w=branch_w)
+            h_next = hc_ops.hc_step(x, self._feed_forward(layer, h2), layer.hc2_mix, layer.hc2_out, in_next, norm_next,
+                                    eps, dt)
+        if self.layer_probe is not None:
+            self.layer_probe(i, x.sum(dim=1).view(B, T, W))
+        return x.view(B, T, SW), (h_next.view(B, T, W) if h_next is not None else None)
 
     def forward_speculation(self, *a, **kw):
         raise NotImplementedError("the speculation verify graph is not wired for this family")

@@ -124,6 +124,24 @@ def _gogalix_cls():
     return GogalixInferenceModel
 
 
+def _vufasun_config(d, dtype):
+    from ..models.vufasun import VufasunConfig
+
+    return VufasunConfig.from_dict(d, torch_dtype=dtype)
+
+
+def _vufasun_convert(sd, cfg):
+    from ..models.vufasun import convert_vufasun_state_dict
+
+    return convert_vufasun_state_dict(sd, cfg)
+
+
+def _vufasun_cls():
+    from .hybrid import VufasunInferenceModel
+
+    return VufasunInferenceModel
+
+
 register_family(ModelFamily("llama", lambda c: _arch(c).startswith("llama"), _llama_config, _llama_cls, _llama_convert))
 register_family(ModelFamily("gekazen", lambda c: _arch(c) == "gekazen", _gekazen_config, _gekazen_cls, _gekazen_convert,
                             kernel_group="window_moe_serving"))
@@ -131,6 +149,8 @@ register_family(ModelFamily("rasodra", lambda c: _arch(c) == "rasodra", _rasodra
                             kernel_group="hybrid_serving"))
 register_family(ModelFamily("gogalix", lambda c: _arch(c) == "gogalix", _gogalix_config, _gogalix_cls, _gogalix_convert,
                             kernel_group="delta_serving"))
+register_family(ModelFamily("vufasun", lambda c: _arch(c) == "vufasun", _vufasun_config, _vufasun_cls, _vufasun_convert,
+                            kernel_group="retention_serving"))
 
 
 def read_config(model_dir: str) -> Dict[str, Any]:

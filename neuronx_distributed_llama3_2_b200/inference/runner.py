@@ -372,3 +372,13 @@ class GogalixRunner(InferenceRunner):
 
         kw.setdefault("model_cls", GogalixInferenceModel)
         super().__init__(*a, **kw)
+
+
+class VufasunRunner(InferenceRunner):
+    """Runner of the Vufasun family (``models/vufasun.py``): same buckets, graphs and generate loop."""
+
+    def __init__(self, *a, **kw):
+        from .hybrid import VufasunInferenceModel
+
+        kw.setdefault("model_cls", VufasunInferenceModel)
+        super().__init__(*a, **kw)

@@ -11,3 +11,5 @@ from .rasodra import (RasodraConfig, RasodraForCausalLM, convert_rasodra_state_d
                       tiny_rasodra)
 from .gogalix import (GogalixConfig, GogalixForCausalLM, convert_gogalix_state_dict, export_gogalix_state_dict,  # noqa: F401
                       tiny_gogalix)
+from .vufasun import (VufasunConfig, VufasunForCausalLM, convert_vufasun_state_dict, export_vufasun_state_dict,  # noqa: F401
+                      tiny_vufasun)

@@ -111,12 +111,13 @@ class RouterBiasedTopK(RouterBase):
     router runs in fp32 whatever the activation dtype; ``select`` is the fused device path (one kernel: projection,
     softmax, choice, optional sigmoid gate of a shared expert).  ``bias``: a bias on the logits (``logit_bias``);
     ``renormalize``: the experts with the largest logits are chosen and their weights are the softmax over the chosen
-    logits only."""
+    logits only; ``score="sigmoid"``: every expert's score is the sigmoid of its own logit instead of the softmax."""
 
     def __init__(self, num_experts: int, top_k: int, hidden_size: int, num_identity_experts: int = 0,
                  affinity_scale: float = 1.0, device: torch.device = torch.device("cpu"), bias: bool = False,
-                 renormalize: bool = False):
-        super().__init__(num_experts + num_identity_experts, top_k, hidden_size, "softmax", torch.float32, device)
+                 renormalize: bool = False, score: str = "softmax"):
+        super().__init__(num_experts + num_identity_experts, top_k, hidden_size, score, torch.float32, device)
+        self.score = score
         self.num_real_experts = num_experts
         self.num_identity_experts = num_identity_experts
         self.affinity_scale = affinity_scale
@@ -132,7 +133,7 @@ class RouterBiasedTopK(RouterBase):
 
         flat = hidden_states.reshape(-1, hidden_states.shape[-1])
         return moe_sparse.route(flat, self.linear_router.weight, self.correction, self.top_k, self.affinity_scale,
-                                shared_gate_weight, self.logit_bias, self.renormalize)
+                                shared_gate_weight, self.logit_bias, self.renormalize, self.score)
 
     def forward(self, hidden_states):
         flat = hidden_states.reshape(-1, hidden_states.shape[-1])

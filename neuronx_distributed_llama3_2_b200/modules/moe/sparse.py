@@ -2,6 +2,9 @@
 the grouped ``Experts`` (clamped gated activation, or the plain ``silu(gate) * up`` with ``limit=None``), optional
 identity experts and an optional gated shared expert.  ``router_bias``: the router has a bias on its logits;
 ``renormalize``: the experts with the largest logits are chosen and weighted by the softmax over the chosen logits only.
+``score="sigmoid"``: every expert's score is the sigmoid of its own logit.  ``weight_on_input``: the routing weight
+multiplies the chosen expert's input instead of its output, ``sum_j expert_j(w_j h)``.  ``shared_gated=False``: the
+shared expert is added as it is, without a sigmoid gate of its own.
 
 Two execution paths over the same parameters:
   * pairs   every (token, choice) pair runs a GEMV against the chosen expert's weights, picked by the index ON THE
@@ -31,8 +34,10 @@ class SparseMoE(torch.nn.Module):
     def __init__(self, hidden_size: int, num_experts: int, top_k: int, intermediate_size: int, limit: float,
                  num_identity_experts: int = 0, affinity_scale: float = 1.0, shared_intermediate_size: int = 0,
                  shared_limit: Optional[float] = None, alpha: float = moe_sparse.GLU_ALPHA,
-                 dtype: torch.dtype = torch.float32, device=None, router_bias: bool = False, renormalize: bool = False):
+                 dtype: torch.dtype = torch.float32, device=None, router_bias: bool = False, renormalize: bool = False,
+                 score: str = "softmax", weight_on_input: bool = False, shared_gated: bool = True):
         super().__init__()
+        self.weight_on_input = weight_on_input
         dev = device if device is not None else torch.device("cpu")
         self.hidden_size, self.num_experts, self.top_k = hidden_size, num_experts, top_k
         if limit is None:            # plain silu(gate) * up: no clamp, unit slope, no shift of the linear half
@@ -42,7 +47,7 @@ class SparseMoE(torch.nn.Module):
         shift = self.up_shift
         self.limit, self.alpha = limit, alpha
         self.router = RouterBiasedTopK(num_experts, top_k, hidden_size, num_identity_experts, affinity_scale, device=dev,
-                                       bias=router_bias, renormalize=renormalize)
+                                       bias=router_bias, renormalize=renormalize, score=score)
         self.experts = Experts(num_experts, hidden_size, intermediate_size, True, None, dtype=dtype, device=dev,
                                glu_fn=lambda gu: moe_sparse.clamped_glu(gu, limit, alpha, shift))
         self.shared = None
@@ -51,7 +56,7 @@ class SparseMoE(torch.nn.Module):
             self.shared_limit = sl
             self.shared = Experts(1, hidden_size, shared_intermediate_size, True, None, dtype=dtype, device=dev,
                                   glu_fn=lambda gu: moe_sparse.clamped_glu(gu, sl, alpha, shift))
-            self.shared_gate = LinearRouter(hidden_size, 1, dtype=torch.float32, device=dev)
+            self.shared_gate = LinearRouter(hidden_size, 1, dtype=torch.float32, device=dev) if shared_gated else None
 
     def _use_sorted(self, n_tokens: int) -> bool:
         # the sorted path reads the per-expert counts on the host: not while a CUDA graph is being captured
@@ -61,18 +66,28 @@ class SparseMoE(torch.nn.Module):
 
     def forward(self, h: torch.Tensor, path: Optional[str] = None) -> torch.Tensor:
         """``h [N, W]`` (activation dtype) -> combined output ``[N, W]`` in fp32."""
-        idx, wts, sg = self.router.select(h, self.shared_gate.weight if self.shared is not None else None)
+        gated = self.shared is not None and self.shared_gate is not None
+        idx, wts, sg = self.router.select(h, self.shared_gate.weight if gated else None)
         sorted_path = self._use_sorted(h.shape[0]) if path is None else path == "sorted"
         if sorted_path:
             return self._forward_sorted(h, idx, wts, sg)
         w_gu, w_d = self.experts.gate_up_proj.weight, self.experts.down_proj.weight
-        act = moe_sparse.gate_up_act(h, w_gu, idx, self.limit, self.alpha, self.up_shift)
+        in_scale = None
+        if self.weight_on_input:            # the weight goes into the expert; the outputs are summed as they are
+            in_scale, wts = wts, self._ones_like(wts)
+        act = moe_sparse.gate_up_act(h, w_gu, idx, self.limit, self.alpha, self.up_shift, in_scale=in_scale)
         s_act = s_down = None
         if self.shared is not None:
             s_act = moe_sparse.gate_up_act(h, self.shared.gate_up_proj.weight, None, self.shared_limit, self.alpha,
                                            self.up_shift)
             s_down = self.shared.down_proj.weight[0]
         return moe_sparse.down_combine(act, w_d, idx, wts, h, s_act, s_down, sg)
+
+    def _ones_like(self, wts: torch.Tensor) -> torch.Tensor:
+        ones = getattr(self, "_ones", None)
+        if ones is None or ones.shape != wts.shape or ones.device != wts.device:
+            ones = self._ones = torch.ones_like(wts)
+        return ones
 
     def _forward_sorted(self, h, idx, wts, sg):
         N, E, k = h.shape[0], self.num_experts, self.top_k
@@ -84,6 +99,9 @@ class SparseMoE(torch.nn.Module):
         slot = torch.empty(N * k, dtype=torch.int32, device=h.device)
         slot[order] = torch.arange(N * k, dtype=torch.int32, device=h.device)
         xs = h[token_of]
+        if self.weight_on_input:
+            xs = (xs.float() * wts.reshape(-1)[order[:n_real]].unsqueeze(1)).to(h.dtype)
+            wts = self._ones_like(wts)
         ys = torch.empty(n_real, h.shape[1], dtype=h.dtype, device=h.device)
         start = 0
         for e, n in enumerate(counts):

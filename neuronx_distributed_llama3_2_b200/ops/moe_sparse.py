@@ -4,6 +4,8 @@ follow the expert index without a host round trip; a clamped gated activation; t
 
     s = softmax(Wr h + b);  chosen = top-k of (s + correction);  weight = s[chosen] * scale
     renormalised form:  chosen = top-k of the logits,  weight = softmax over the chosen logits only
+    sigmoid form:       s = sigmoid(Wr h + b) per expert, then as the first form
+    the weight multiplies the expert's output, or (``in_scale``) its input:  sum_j expert_j(w_j h)
     act(g, u) = g' * sigmoid(alpha * g') * (u' + shift),  g' = min(g, limit),  u' = clamp(u, -limit, limit)
     (limit = inf, alpha = 1, shift = 0 is the plain silu(g) * u)
     expert index >= E: identity expert (output = input)
@@ -33,9 +35,11 @@ def _use_kernel(x: torch.Tensor) -> bool:
 
 
 def clamped_glu_ref(gate: torch.Tensor, up: torch.Tensor, limit: float, alpha: float = GLU_ALPHA,
-                    up_shift: float = 1.0) -> torch.Tensor:
+                    up_shift: float = 1.0, act: str = "sigmoid") -> torch.Tensor:
     g = gate.float().clamp(max=limit)
     u = up.float().clamp(-limit, limit)
+    if act == "gelu_tanh":
+        return (torch.nn.functional.gelu(g, approximate="tanh") * (u + up_shift)).to(gate.dtype)
     return (g * torch.sigmoid(alpha * g) * (u + up_shift)).to(gate.dtype)
 
 
@@ -55,9 +59,10 @@ def clamped_glu(gate_up: torch.Tensor, limit: float, alpha: float = GLU_ALPHA, u
 
 def glu_bias(src: torch.Tensor, gate_offset: int, up_offset: int, width: int, gate_bias: Optional[torch.Tensor] = None,
              up_bias: Optional[torch.Tensor] = None, limit: Optional[float] = None, alpha: float = GLU_ALPHA,
-             up_shift: float = 1.0) -> torch.Tensor:
+             up_shift: float = 1.0, act: str = "sigmoid") -> torch.Tensor:
     """Gated activation whose gate and up halves are column ranges of a wider projection output ``src [M, ld]``, each
-    with an optional fp32 bias -> ``[M, width]``.  ``limit=None``: the plain ``silu(gate) * up``."""
+    with an optional fp32 bias -> ``[M, width]``.  ``limit=None``: the plain ``silu(gate) * up``; ``act="gelu_tanh"``:
+    the gate goes through the tanh form of gelu, ``0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3)))``."""
     if limit is None:
         limit, alpha, up_shift = float("inf"), 1.0, 0.0
     M = src.shape[0]
@@ -68,7 +73,8 @@ def glu_bias(src: torch.Tensor, gate_offset: int, up_offset: int, width: int, ga
         L = _lib.lib(GROUP)
         rc = L.nxd_glu_bias(_c.c_int(_code(src.dtype)), _lib.ptr(src), _c.c_longlong(src.stride(0)), _c.c_int(gate_offset),
                             _c.c_int(up_offset), _lib.ptr(gb), _lib.ptr(ub), _lib.ptr(out), _c.c_longlong(M),
-                            _c.c_int(width), _c.c_float(limit), _c.c_float(alpha), _c.c_float(up_shift), _lib.stream_ptr())
+                            _c.c_int(width), _c.c_float(limit), _c.c_float(alpha), _c.c_float(up_shift),
+                            _c.c_int(1 if act == "gelu_tanh" else 0), _lib.stream_ptr())
         _lib.check(rc, "nxd_glu_bias", L)
         return out
     g = src[:, gate_offset: gate_offset + width].float()
@@ -77,15 +83,17 @@ def glu_bias(src: torch.Tensor, gate_offset: int, up_offset: int, width: int, ga
         g = g + gate_bias.float()
     if up_bias is not None:
         u = u + up_bias.float()
-    return clamped_glu_ref(g, u, limit, alpha, up_shift).to(src.dtype)
+    return clamped_glu_ref(g, u, limit, alpha, up_shift, act).to(src.dtype)
 
 
 def route(h: torch.Tensor, router_w: torch.Tensor, correction: Optional[torch.Tensor], top: int, scale: float,
           shared_gate_w: Optional[torch.Tensor] = None, logit_bias: Optional[torch.Tensor] = None,
-          renormalize: bool = False) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
+          renormalize: bool = False, score: str = "softmax") -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
     """``h [N, W]``, ``router_w [R, W]`` fp32 -> ``(index [N, top] int32, weight [N, top] fp32, shared gate [N] fp32)``.
     ``logit_bias [R]`` is added to the logits; ``renormalize``: the largest logits are chosen and weighted by the softmax
-    over the chosen logits only (``correction`` does not apply)."""
+    over the chosen logits only (``correction`` does not apply); ``score="sigmoid"``: every expert's score is the sigmoid
+    of its own logit instead of the softmax over all of them."""
+    assert score in ("softmax", "sigmoid") and not (renormalize and score == "sigmoid")
     N, W = h.shape
     R = router_w.shape[0]
     if _use_kernel(h) and router_w.dtype == torch.float32:
@@ -99,8 +107,8 @@ def route(h: torch.Tensor, router_w: torch.Tensor, correction: Optional[torch.Te
         L = _lib.lib(GROUP)
         rc = L.nxd_moe_router(_c.c_int(_code(h.dtype)), _lib.ptr(h), _lib.ptr(router_w.contiguous()), _lib.ptr(corr),
                               _lib.ptr(wsg), _lib.ptr(idx), _lib.ptr(wts), _lib.ptr(sg), _c.c_longlong(N), _c.c_int(W),
-                              _c.c_int(R), _c.c_int(top), _c.c_float(scale), _lib.ptr(zb), _c.c_int(int(renormalize)),
-                              _lib.stream_ptr())
+                              _c.c_int(R), _c.c_int(top), _c.c_float(scale), _lib.ptr(zb),
+                              _c.c_int(2 if score == "sigmoid" else int(renormalize)), _lib.stream_ptr())
         _lib.check(rc, "nxd_moe_router", L)
         return idx, wts, sg
     hf = h.float()
@@ -111,7 +119,7 @@ def route(h: torch.Tensor, router_w: torch.Tensor, correction: Optional[torch.Te
     if renormalize:
         val, idx = torch.topk(z, top, dim=-1)
         return idx.to(torch.int32), torch.softmax(val, dim=-1) * scale, sg
-    s = torch.softmax(z, dim=-1)
+    s = torch.sigmoid(z) if score == "sigmoid" else torch.softmax(z, dim=-1)
     choice = s + correction.float() if correction is not None else s
     idx = torch.topk(choice, top, dim=-1).indices
     wts = s.gather(1, idx) * scale
@@ -119,9 +127,10 @@ def route(h: torch.Tensor, router_w: torch.Tensor, correction: Optional[torch.Te
 
 
 def gate_up_act(h: torch.Tensor, w_gate_up: torch.Tensor, idx: Optional[torch.Tensor], limit: float,
-                alpha: float = GLU_ALPHA, up_shift: float = 1.0) -> torch.Tensor:
+                alpha: float = GLU_ALPHA, up_shift: float = 1.0, in_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Activated intermediate of every (token, choice) pair: ``h [N, W]``, ``w_gate_up [E, W, 2F]``, ``idx [N, top]`` (or
-    ``None``: one dense expert, ``top = 1``) -> ``[N * top, F]``.  Rows of identity experts are left untouched (zeros)."""
+    ``None``: one dense expert, ``top = 1``) -> ``[N * top, F]``.  Rows of identity experts are left untouched (zeros).
+    ``in_scale [N, top]`` fp32: the pair's input row is multiplied by it (in fp32) before the products."""
     N, W = h.shape
     E, _, F2 = w_gate_up.shape
     F = F2 // 2
@@ -129,11 +138,12 @@ def gate_up_act(h: torch.Tensor, w_gate_up: torch.Tensor, idx: Optional[torch.Te
     if _use_kernel(h) and w_gate_up.dtype == h.dtype:
         h = h if h.is_contiguous() else h.contiguous()
         act = torch.zeros(N * top, F, dtype=h.dtype, device=h.device)
+        isc = in_scale.float().contiguous() if in_scale is not None else None
         L = _lib.lib(GROUP)
         rc = L.nxd_moe_gate_up_act(_c.c_int(_code(h.dtype)), _lib.ptr(h), _lib.ptr(w_gate_up), _lib.ptr(idx),
                                    _lib.ptr(act), _c.c_longlong(N * top), _c.c_int(top), _c.c_int(W), _c.c_int(F),
                                    _c.c_int(E), _c.c_float(limit), _c.c_float(alpha), _c.c_float(up_shift),
-                                   _lib.stream_ptr())
+                                   _lib.ptr(isc), _lib.stream_ptr())
         _lib.check(rc, "nxd_moe_gate_up_act", L)
         return act
     act = torch.zeros(N * top, F, dtype=h.dtype, device=h.device)
@@ -142,7 +152,10 @@ def gate_up_act(h: torch.Tensor, w_gate_up: torch.Tensor, idx: Optional[torch.Te
     for e in range(E):
         rows = (e_of == e).nonzero().reshape(-1)
         if rows.numel():
-            gu = h[tok[rows]].float() @ w_gate_up[e].float()
+            x = h[tok[rows]].float()
+            if in_scale is not None:
+                x = x * in_scale.reshape(-1)[rows].float().unsqueeze(1)
+            gu = x @ w_gate_up[e].float()
             act[rows] = clamped_glu_ref(gu[:, :F], gu[:, F:], limit, alpha, up_shift).to(h.dtype)
     return act
 

@@ -42,12 +42,26 @@ def build_rope_cache(max_pos: int, head_dim: int, theta: float = 500000.0, rope_
     return freqs.cos().contiguous(), freqs.sin().contiguous()
 
 
-def build_interleaved_rope_cache(max_pos: int, dims: int, base: float, device=None) -> Tuple[torch.Tensor, torch.Tensor]:
+def wavelength_scaled_frequencies(freq: torch.Tensor, factor: float, low: float, high: float, original: float) -> torch.Tensor:
+    """The Llama-3.1 slowdown of long waves (``llama3_scale_inv_freq`` above, in the dtype of ``freq``): with wavelength
+    ``l = 2 pi / f``, ``f`` stays where ``l < original / high``, becomes ``f / factor`` where ``l > original / low``, and
+    in between ``(1 - s) f / factor + s f`` with ``s = (original / l - low) / (high - low)``."""
+    wave = 2.0 * math.pi / freq
+    s = (original / wave - low) / (high - low)
+    mid = (1.0 - s) * freq / factor + s * freq
+    return torch.where(wave < original / high, freq, torch.where(wave > original / low, freq / factor, mid))
+
+
+def build_interleaved_rope_cache(max_pos: int, dims: int, base: float, device=None,
+                                 scaling: Optional[Tuple[float, float, float, float]] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """fp32 ``cos`` / ``sin`` tables ``[max_pos, dims/2]`` of the angles ``p * base ** (-2 i / dims)``, evaluated in
-    float64 (a position of a few thousand times a frequency loses digits of the angle in fp32)."""
+    float64 (a position of a few thousand times a frequency loses digits of the angle in fp32).  ``scaling = (factor, low,
+    high, original)``: the frequencies first go through ``wavelength_scaled_frequencies``."""
     i = torch.arange(dims // 2, dtype=torch.float64)
-    ang = torch.outer(torch.arange(max_pos, dtype=torch.float64), torch.pow(torch.tensor(float(base), dtype=torch.float64),
-                                                                             -2.0 * i / dims))
+    freq = torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / dims)
+    if scaling is not None:
+        freq = wavelength_scaled_frequencies(freq, *[float(x) for x in scaling])
+    ang = torch.outer(torch.arange(max_pos, dtype=torch.float64), freq)
     return ang.cos().float().contiguous().to(device), ang.sin().float().contiguous().to(device)
 
 
@@ -62,6 +76,16 @@ def rope_interleaved_ref(x: torch.Tensor, positions: torch.Tensor, cos: torch.Te
     out[..., 0:rot:2] = u * c - v * s
     out[..., 1:rot:2] = v * c + u * s
     return out
+
+
+def rope_halves_ref(x: torch.Tensor, positions: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """As ``rope_interleaved_ref`` with the pairs ``(i, i + rot/2)`` ("rotate half" layout) of the first ``rot =
+    2 * cos.shape[1]`` dimensions."""
+    half = cos.shape[1]
+    c = cos[positions.long()].unsqueeze(-2).to(x.dtype)
+    s = sin[positions.long()].unsqueeze(-2).to(x.dtype)
+    u, v = x[..., :half], x[..., half: 2 * half]
+    return torch.cat([u * c - v * s, v * c + u * s, x[..., 2 * half:]], dim=-1)
 
 
 def _positions(T: int, pos_div: int, pos_mod: int, positions, device):

@@ -77,11 +77,15 @@ def qk_norm_cache_write(qkv: torch.Tensor, cache_k: Optional[torch.Tensor], cach
                         normalize: bool = True, block_table: Optional[torch.Tensor] = None,
                         page_size: int = 0, writeback: bool = False, q_weight: Optional[torch.Tensor] = None,
                         k_weight: Optional[torch.Tensor] = None, rope: Optional[tuple] = None,
-                        value_from_key: bool = False, value_heads: Optional[int] = None) -> torch.Tensor:
+                        value_from_key: bool = False, value_heads: Optional[int] = None, rope_layout: str = "pairs",
+                        whole_norm: bool = False) -> torch.Tensor:
     """``q_weight / k_weight [dim]``: weight of the per-head norm (after the division).  ``rope = (cos, sin)`` tables
     ``[positions, rot/2]`` (``ops.rope.build_interleaved_rope_cache``): queries and keys turn pairwise on their first
-    ``rot`` dimensions, after the norm.  ``value_from_key``: the projection has no value columns, the cached value is
-    the raw key projection (taken ahead of the norm and the rotation).
+    ``rot`` dimensions, after the norm; pair ``i`` is the dimensions ``(2i, 2i + 1)`` (``rope_layout="pairs"``) or
+    ``(i, i + rot/2)`` (``"halves"``).  ``value_from_key``: the projection has no value columns, the cached value is
+    the raw key projection (taken ahead of the norm and the rotation).  ``whole_norm``: the root mean square is taken
+    over ALL query heads of a row at once (and over all its key heads), and ``q_weight [heads * dim]`` /
+    ``k_weight [kv_heads * dim]`` cover the whole projection.
 
     ``qkv [B, T, heads*dim (+ kv_heads*dim + kv_heads*vdim)]`` -> ``q [B, T, heads, dim]``; with a cache given the
     key and value heads of the real rows (``t < n_new[b]``) are written at position ``q_start[b] + t`` of cache line
@@ -118,7 +122,9 @@ def qk_norm_cache_write(qkv: torch.Tensor, cache_k: Optional[torch.Tensor], cach
                                        _c.c_int(vdim), _c.c_int(int(has_kv)), _c.c_int(int(normalize)), _c.c_float(eps),
                                        _c.c_int(max_pos), _c.c_int(int(writeback and has_kv)), _lib.ptr(qw), _lib.ptr(kw),
                                        _lib.ptr(cos), _lib.ptr(sin), _c.c_int(2 * cos.shape[1] if cos is not None else 0),
-                                       _c.c_int(int(value_from_key)), _c.c_int(gv), _lib.stream_ptr())
+                                       _c.c_int(int(value_from_key)), _c.c_int(gv),
+                                       _c.c_int(int(rope_layout == "halves")), _c.c_int(int(whole_norm)),
+                                       _lib.stream_ptr())
         _lib.check(rc, "nxd_qk_prep_cache_write", L)
         return q
 
@@ -126,14 +132,16 @@ def qk_norm_cache_write(qkv: torch.Tensor, cache_k: Optional[torch.Tensor], cach
 
     def unit(x, w):
         xf = x.float()
-        if normalize:
+        if normalize and whole_norm:
+            xf = xf / torch.sqrt(xf.pow(2).mean((-2, -1), keepdim=True) + eps)
+        elif normalize:
             xf = xf / torch.sqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
         if w is not None:
-            xf = xf * w.float()
+            xf = xf * (w.float().reshape(xf.shape[-2:]) if whole_norm else w.float())
         if rope is not None:
-            from .rope import rope_interleaved_ref
+            from .rope import rope_halves_ref, rope_interleaved_ref
 
-            xf = rope_interleaved_ref(xf, pos_bt, rope[0], rope[1])
+            xf = (rope_halves_ref if rope_layout == "halves" else rope_interleaved_ref)(xf, pos_bt, rope[0], rope[1])
         return xf.to(x.dtype)
 
     q = unit(qkv[..., : heads * dim].reshape(B, T, heads, dim), q_weight)
