@@ -55,10 +55,11 @@ def parse_args():
     ap.add_argument("--no-inference", action="store_true",
                     help="skip the second half of the headline metric (Llama-3.2-1B TTFT / decode tokens/s, reported "
                          "under the extra key \"inference\")")
-    ap.add_argument("--families", nargs="?", const="gekazen", default="", choices=["gekazen", "rasodra", "gogalix"],
+    ap.add_argument("--families", nargs="?", const="gekazen", default="", choices=["gekazen", "rasodra", "gogalix", "vufasun"],
                     help="instead of the headline workload: serving throughput (prefill and decode tokens/s) of a "
                          "family next to the closest existing decoder at equal layer sizes (gekazen: the Mixtral-style "
-                         "decoder; rasodra: the Llama decoder; gogalix: the Rasodra hybrid), and their like-for-like kernels with roofline fractions "
+                         "decoder; rasodra: the Llama decoder; gogalix: the Rasodra hybrid; vufasun: the Gogalix hybrid), and their like-for-like "
+                         "kernels with roofline fractions "
                          "(1 GPU; one JSON line)")
     ap.add_argument("--profile", default="", help="diagnosis only: write a kernel timeline summary of 2 steps (rank 0) "
                     "to this file instead of timing (numbers under a profiler are never bench values)")
@@ -436,8 +437,8 @@ def main():
         assert world == 1, "--families is a single-GPU comparison"
         sampler = ClockSampler(local_rank)
         sampler.start()
-        bench_fn = {"rasodra": family_bench.run_hybrid, "gogalix": family_bench.run_delta}.get(args.families,
-                                                                                             family_bench.run)
+        bench_fn = {"rasodra": family_bench.run_hybrid, "gogalix": family_bench.run_delta,
+                    "vufasun": family_bench.run_retention}.get(args.families, family_bench.run)
         out = bench_fn(steps=args.steps, warmup=args.warmup, device=dev)
         out["clocks"] = sampler.stop()
         print(json.dumps(out))

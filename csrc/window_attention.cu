@@ -46,6 +46,31 @@ __device__ __forceinline__ void stf(float* p, float v) { *p = v; }
 __device__ __forceinline__ void stf(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
 
 // ---------------------------------------------------------------------------------------------------------------------
+// 1 / rms over all query heads (stat[2n]) and over all key heads (stat[2n + 1]) of projection row n: one warp per row
+template <typename T>
+__global__ void qk_row_stat_kernel(const T* __restrict__ qkv, long long ld, float* __restrict__ stat, long long rows, int nq,
+                                   int nk, float eps) {
+    const int lane = threadIdx.x & 31;
+    const long long n = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (n >= rows) return;
+    const T* row = qkv + n * ld;
+    float sq = 0.f, sk = 0.f;
+    for (int i = lane; i < nq; i += 32) {
+        const float v = ldf(row + i);
+        sq += v * v;
+    }
+    for (int i = lane; i < nk; i += 32) {
+        const float v = ldf(row + nq + i);
+        sk += v * v;
+    }
+    sq = warp_sum(sq);
+    sk = warp_sum(sk);
+    if (lane == 0) {
+        stat[2 * n] = 1.f / sqrtf(sq / (float)nq + eps);
+        stat[2 * n + 1] = nk > 0 ? 1.f / sqrtf(sk / (float)nk + eps) : 1.f;
+    }
+}
+
 template <typename T>
 __global__ void qk_norm_cache_write_kernel(const T* __restrict__ qkv, long long ld, T* __restrict__ q_out,
                                            T* __restrict__ cache_k, T* __restrict__ cache_v, CacheAddr ka, CacheAddr va,
@@ -55,7 +80,7 @@ __global__ void qk_norm_cache_write_kernel(const T* __restrict__ qkv, long long 
                                            const float* __restrict__ q_weight, const float* __restrict__ k_weight,
                                            const float* __restrict__ rope_cos, const float* __restrict__ rope_sin,
                                            int rope_dims, int value_from_key, int Gv, int rope_halves,
-                                           int whole_norm) {
+                                           int whole_norm, const float* __restrict__ row_stat) {
     const int lane = threadIdx.x & 31;
     const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (unit >= units) return;
@@ -89,7 +114,9 @@ __global__ void qk_norm_cache_write_kernel(const T* __restrict__ qkv, long long 
         dst = hd < H + G ? cache_k + ka.row(line, hd - H, pos) : cache_v + va.row(line, hd - H - G, pos);
     }
     float r = 1.f;
-    if (hd < H + G && normalize) {
+    if (hd < H + G && normalize && whole_norm && row_stat != nullptr) {
+        r = row_stat[2 * n + (hd < H ? 0 : 1)];               // computed once per row by qk_row_stat_kernel
+    } else if (hd < H + G && normalize) {
         // whole_norm: the statistic runs over all heads of the projection (queries: H * D values, keys: G * D) and the
         // weight has that size; else over the head alone, with a weight of D values shared by the heads
         const T* stat = whole_norm ? (hd < H ? qkv + n * ld : qkv + n * ld + (long long)H * D) : src;
@@ -931,7 +958,8 @@ int launch_decode(const void* q, const void* ck, const void* cv, CacheAddr ka, C
 // q_weight / k_weight [D] fp32 or NULL: weight of the per-head norm.  rope_cos / rope_sin [positions, rope_dims / 2]
 // fp32 or NULL: queries and keys (after the norm) turn pairwise, (2i, 2i + 1), on their first rope_dims dimensions
 // (rope_halves: the pairs are (i, i + rope_dims / 2)).  whole_norm: the norm's statistic runs over all query heads (all
-// key heads) of a row at once and q_weight / k_weight hold H * D / G * D values.
+// key heads) of a row at once and q_weight / k_weight hold H * D / G * D values; row_stat [B * Tn, 2] fp32 scratch (or NULL:
+// every head's warp computes the row statistic itself).
 // value_from_key: the row has no value columns, the cached value is the raw key projection (taken ahead of the norm and the rotation).
 NXD_API int nxd_qk_prep_cache_write(int dtype, const void* qkv, long long ld, void* q_out, void* cache_k, void* cache_v,
                                     long long k_stride_line, long long k_stride_head, long long v_stride_line,
@@ -940,7 +968,7 @@ NXD_API int nxd_qk_prep_cache_write(int dtype, const void* qkv, long long ld, vo
                                     int D, int Dv, int has_kv, int normalize, float eps, int max_pos, int writeback,
                                     const float* q_weight, const float* k_weight, const float* rope_cos,
                                     const float* rope_sin, int rope_dims, int value_from_key, int value_heads,
-                                    int rope_halves, int whole_norm, void* stream) {
+                                    int rope_halves, int whole_norm, float* row_stat, void* stream) {
     const int Gv = value_heads > 0 ? value_heads : G;
     const long long units = (long long)B * Tn * (H + (has_kv ? G + Gv : 0));
     if (units == 0) return 0;
@@ -952,16 +980,28 @@ NXD_API int nxd_qk_prep_cache_write(int dtype, const void* qkv, long long ld, vo
     const CacheAddr va = make_addr(v_stride_line, v_stride_head, block_table, page_size, table_cols, Dv);
     const int wpb = 8;
     const unsigned blocks = (unsigned)((units + wpb - 1) / wpb);
+    if (!(whole_norm && normalize)) row_stat = nullptr;
+    if (row_stat != nullptr) {           // the whole-projection statistics once per row, ahead of the per-head warps
+        const long long rows = (long long)B * Tn;
+        const unsigned sb = (unsigned)((rows + wpb - 1) / wpb);
+        if (dtype == 0)
+            qk_row_stat_kernel<bf16><<<sb, wpb * 32, 0, (cudaStream_t)stream>>>((const bf16*)qkv, ld, row_stat, rows, H * D,
+                                                                                has_kv ? G * D : 0, eps);
+        else
+            qk_row_stat_kernel<float><<<sb, wpb * 32, 0, (cudaStream_t)stream>>>((const float*)qkv, ld, row_stat, rows, H * D,
+                                                                                 has_kv ? G * D : 0, eps);
+        NXD_LAUNCH_CHECK();
+    }
     if (dtype == 0)
         qk_norm_cache_write_kernel<bf16><<<blocks, wpb * 32, 0, (cudaStream_t)stream>>>(
             (const bf16*)qkv, ld, (bf16*)q_out, (bf16*)cache_k, (bf16*)cache_v, ka, va, q_start, n_new, seq_ids, units, Tn,
             H, G, D, Dv, has_kv, normalize, eps, max_pos, writeback, q_weight, k_weight, rope_cos, rope_sin, rope_dims,
-            value_from_key, Gv, rope_halves, whole_norm);
+            value_from_key, Gv, rope_halves, whole_norm, row_stat);
     else
         qk_norm_cache_write_kernel<float><<<blocks, wpb * 32, 0, (cudaStream_t)stream>>>(
             (const float*)qkv, ld, (float*)q_out, (float*)cache_k, (float*)cache_v, ka, va, q_start, n_new, seq_ids, units,
             Tn, H, G, D, Dv, has_kv, normalize, eps, max_pos, writeback, q_weight, k_weight, rope_cos, rope_sin, rope_dims,
-            value_from_key, Gv, rope_halves, whole_norm);
+            value_from_key, Gv, rope_halves, whole_norm, row_stat);
     NXD_LAUNCH_CHECK();
     return 0;
 }
@@ -975,7 +1015,7 @@ NXD_API int nxd_qk_norm_cache_write(int dtype, const void* qkv, long long ld, vo
     return nxd_qk_prep_cache_write(dtype, qkv, ld, q_out, cache_k, cache_v, k_stride_line, k_stride_head, v_stride_line,
                                    v_stride_head, block_table, page_size, table_cols, q_start, n_new, seq_ids, B, Tn, H, G,
                                    D, Dv, has_kv, normalize, eps, max_pos, writeback, nullptr, nullptr, nullptr, nullptr, 0,
-                                   0, 0, 0, 0, stream);
+                                   0, 0, 0, 0, nullptr, stream);
 }
 
 // q [B, Tn, H, D] -> out [B, Tn, H, Dv]; the keys and values of positions [0, q_start[b] + n_new[b]) are read from the

@@ -306,7 +306,8 @@ int nxd_window_attn_decode(int dtype, const void* q, const void* cache_k, const 
  * k_row when the values are columns of the key rows).  nxd_qk_prep_cache_write adds norm weights (fp32 [D] or NULL),
  * pairwise rotation from cos / sin tables [positions, rope_dims / 2] (pairs (2i, 2i + 1), or with rope_halves
  * (i, i + rope_dims / 2)), value_from_key (cached value = raw key) and whole_norm (the norm's statistic over all query /
- * all key heads of a row at once, weights of H * D / G * D values). */
+ * all key heads of a row at once, weights of H * D / G * D values; row_stat [B * Tn, 2] fp32 scratch for the statistics,
+ * or NULL). */
 int nxd_qk_prep_cache_write(int dtype, const void* qkv, long long ld, void* q_out, void* cache_k, void* cache_v,
                             long long k_stride_line, long long k_stride_head, long long v_stride_line,
                             long long v_stride_head, const int* block_table, int page_size, int table_cols,
@@ -314,7 +315,7 @@ int nxd_qk_prep_cache_write(int dtype, const void* qkv, long long ld, void* q_ou
                             int Dv, int has_kv, int normalize, float eps, int max_pos, int writeback,
                             const float* q_weight, const float* k_weight, const float* rope_cos, const float* rope_sin,
                             int rope_dims, int value_from_key, int value_heads, int rope_halves, int whole_norm,
-                            void* stream);
+                            float* row_stat, void* stream);
 /* value_heads (0 = as many as key heads): head g of the value cache serves the key heads g, g + value_heads, ...
  * (several attention maps over the same values); the projection row then holds value_heads value heads. */
 int nxd_masked_attn_prefill(int dtype, const void* q, const void* cache_k, const void* cache_v, long long k_stride_line,

@@ -590,3 +590,180 @@ def run_delta(steps: int = 10, warmup: int = 3, device=None, sizes=None) -> dict
         out["kernels"][s["name"]] = delta_kernel_cases(s, steps, warmup, dev)
     out["gpu_launches"] = _lib.kernel_launches() - before
     return out
+
+
+# ---- Vufasun next to Gogalix ------------------------------------------------------------------------------------------------
+VUFASUN_STREAMS = 2
+
+
+def vufasun_config(s: dict):
+    from ..models.vufasun import VufasunConfig
+
+    # gate, up and down of (width x f), as in Gogalix's dense feed-forward: the same f keeps the parameters equal
+    ff = {"kind": "dense", "ff": (2 * s["ff"] // 3 + 127) // 128 * 128}
+    rot = {"base": 500000.0, "dims": s["dim"] // 2}
+    att = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"], "scale": s["dim"] ** -0.5,
+           "rot": rot}
+    left = dict(att, rot=dict(rot, scaling={"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}))
+    decay = [1.0 - 2.0 ** (-5 - 3.0 * h / max(s["rec_heads"] - 1, 1)) for h in range(s["rec_heads"])]
+    right = {"heads": s["rec_heads"], "dim": s["rec_dim"], "vdim": s["rec_vdim"], "decay": decay,
+             "rot": {"base": 500000.0, "dims": s["rec_dim"]}}
+    par = {"left": left, "right": right}
+    return VufasunConfig.from_dict({
+        "architecture": "Vufasun", "vocab": VOCAB, "width": s["width"], "streams": VUFASUN_STREAMS, "norm": {"eps": 1e-6},
+        "layers": [{"type": "parallel", "mixer": par, "mlp": ff},
+                   {"type": "attention", "mixer": att, "mlp": ff},
+                   {"type": "parallel", "mixer": par, "mlp": ff}]}, torch_dtype=torch.bfloat16)
+
+
+def retention_serve_case(s: dict, steps: int, warmup: int, dev) -> dict:
+    from .hybrid import GogalixInferenceModel, VufasunInferenceModel
+
+    timer = _Timer(dev)
+    out = {"size": dict(s)}
+    ic = dict(batch_size=s["decode_batch"], max_batch_size=s["decode_batch"], max_context_length=s["prompt"],
+              seq_len=s["prompt"] + 64, is_continuous_batching=True, use_cuda_graphs=False)
+    for name, make in (("vufasun", lambda: VufasunInferenceModel(vufasun_config(s), InferenceConfig(**ic), device=dev)),
+                       ("gogalix", lambda: GogalixInferenceModel(gogalix_config(s), InferenceConfig(**ic), device=dev))):
+        torch.manual_seed(0)
+        model = make()
+        model.init_kv_cache(device=dev)
+        out[name] = _serve(model, s, timer, steps, warmup, dev)
+        out[name]["parameters"] = sum(p.numel() for p in model.parameters())
+        del model
+        torch.cuda.empty_cache()
+    out["vufasun_over_gogalix"] = {k: out["vufasun"][k] / out["gogalix"][k]
+                                   for k in ("prefill_tokens_per_s", "decode_tokens_per_s")}
+    return out
+
+
+def retention_kernel_cases(s: dict, steps: int, warmup: int, dev) -> List[dict]:
+    """Vufasun's own kernels on the shapes of ``s``, alone, with roofline fractions, each next to the like kernel of the
+    Gogalix / Rasodra families (recurrent scan / step, attention over the cache, residual update, projection epilogue)."""
+    from ..ops import hyper_connection as hc_ops
+    from ..ops import mlstm as ml
+    from ..ops import retention as rt
+    from ..ops import rope as rope_ops
+
+    pk = peaks()
+    timer = _Timer(dev)
+    bf = torch.bfloat16
+    B, T, H, G, D, W, Bd = s["prefill_batch"], s["prompt"], s["heads"], s["kv_heads"], s["dim"], s["width"], s["decode_batch"]
+    rows = []
+
+    def row(kernel, like, ms, flops=None, nbytes=None):
+        r = {"kernel": kernel, "like": like, "ms": ms, "peak": pk["source"]}
+        if flops is not None:
+            r["tflops"] = flops / ms / 1e9
+            r["of_peak"] = r["tflops"] / pk["bf16_tflops"]
+        if nbytes is not None:
+            r["gbs"] = nbytes / ms / 1e6
+            r["of_peak"] = r["gbs"] / pk["hbm_gbs"]
+        rows.append(r)
+
+    S, N = T + 64, B * T
+    zero = torch.zeros(B, dtype=torch.int32, device=dev)
+    pairs = T * (T + 1) // 2
+    # softmax attention with the sink term, next to the same kernels without it
+    q = torch.randn(B, T, H, D, device=dev, dtype=bf)
+    ck = torch.randn(max(B, Bd), G, S, D, device=dev, dtype=bf)
+    cv = torch.randn(max(B, Bd), G, S, D, device=dev, dtype=bf)
+    sink = torch.randn(H, device=dev)
+    for name, sk in (("softmax attention prefill with a sink term, over the cache", sink),
+                     ("causal attention prefill over the cache (the like kernel)", None)):
+        ms = timer(lambda: wa.window_attention_prefill(q, ck, cv, zero, D ** -0.5, sinks=sk), steps, warmup)
+        row(name, "prefill attention", ms, flops=4.0 * D * pairs * H * B)
+    qd = torch.randn(Bd, H, D, device=dev, dtype=bf)
+    posd = torch.full((Bd,), T, dtype=torch.int32, device=dev)
+    for name, sk in (("softmax attention decode with a sink term", sink), ("causal attention decode (the like kernel)", None)):
+        ms = timer(lambda: wa.window_attention_decode(qd, ck, cv, posd, D ** -0.5, sinks=sk), steps, warmup)
+        row(name, "decode attention", ms, nbytes=2.0 * (T + 1) * G * 2 * D * Bd)
+    n_qkv = H * D + 2 * G * D
+    wide = torch.randn(B, T, n_qkv, device=dev, dtype=bf)
+    ckw, cvw = torch.zeros(B, G, S, D, device=dev, dtype=bf), torch.zeros(B, G, S, D, device=dev, dtype=bf)
+    rope = rope_ops.build_interleaved_rope_cache(S, D // 2, 500000.0, device=dev, scaling=(8.0, 1.0, 4.0, 8192))
+    qw, kw = torch.ones(H * D, device=dev), torch.ones(G * D, device=dev)
+    ms = timer(lambda: wa.qk_norm_cache_write(wide, ckw, cvw, zero, H, G, D, D, 1e-6, normalize=True, q_weight=qw,
+                                              k_weight=kw, rope=rope, rope_layout="halves", whole_norm=True), steps, warmup)
+    row("whole-projection q / k norm + rotation of halves + cache write", "projection epilogue", ms,
+        nbytes=2.0 * N * (2 * H * D + 4 * G * D))
+    ms = timer(lambda: wa.qk_norm_cache_write(wide, ckw, cvw, zero, H, G, D, D, 1e-6, normalize=False, rope=rope,
+                                              rope_layout="halves"), steps, warmup)
+    row("rotation of halves + cache write (sink-attention layers)", "projection epilogue", ms,
+        nbytes=2.0 * N * (2 * H * D + 4 * G * D))
+    ms = timer(lambda: wa.qk_norm_cache_write(wide, ckw, cvw, zero, H, G, D, D, 1e-6, normalize=True), steps, warmup)
+    row("per-head unit norm + cache write (the like kernel)", "projection epilogue", ms,
+        nbytes=2.0 * N * (2 * H * D + 4 * G * D))
+    del q, ck, cv, wide, ckw, cvw
+    # retention next to the matrix-memory kernels
+    Hr, Dk, Dvr = s["rec_heads"], s["rec_dim"], s["rec_vdim"]
+    ld = 2 * Hr * Dk + 2 * Hr * Dvr
+    pr = torch.randn(B, T, ld, device=dev, dtype=bf) * 0.3
+    dec = torch.full((Hr,), 0.99, device=dev)
+    st = torch.zeros(max(B, Bd), Hr, Dk, Dvr, device=dev)
+    rrope = rope_ops.build_interleaved_rope_cache(S, Dk, 500000.0, device=dev)
+    offs = (0, Hr * Dk, 2 * Hr * Dk)
+    flops = 4.0 * Dk * Dvr * Hr * B * T
+    if rt.chunkwise_applies(Dk, Dvr):
+        ms = timer(lambda: rt.retention_chunkwise(pr, offs, dec, st, zero, Hr, Dk, Dvr, Dk ** -0.5, rope=rrope), steps, warmup)
+        row("retention prompt, chunk-wise (rotation inside)", "prefill attention", ms, flops=flops)
+    ms = timer(lambda: rt.retention_scan(pr, offs, dec, st, zero, Hr, Dk, Dvr, Dk ** -0.5, rope=rrope), steps, warmup)
+    row("retention prompt, token by token (state slice in registers, rotation inside)", "prefill attention", ms, flops=flops)
+    gi, gf = torch.randn(N, Hr, device=dev), -torch.rand(N, Hr, device=dev) * 0.1
+    mst = (torch.zeros(max(B, Bd), Hr, Dk, Dvr, device=dev), torch.zeros(max(B, Bd), Hr, Dk, device=dev),
+           torch.zeros(max(B, Bd), Hr, device=dev))
+    ms = timer(lambda: ml.mlstm_scan(pr, offs, gi, gf, mst, zero, Hr, Dk, Dvr, Dk ** -0.5), steps, warmup)
+    row("matrix-memory scan, prompt, token by token (the like kernel)", "prefill attention", ms, flops=flops)
+    ms = timer(lambda: ml.mlstm_chunkwise(pr, offs, gi, gf, mst, zero, Hr, Dk, Dvr, Dk ** -0.5), steps, warmup)
+    row("matrix-memory prompt, chunk-wise (the like kernel of long bf16 steps)", "prefill attention", ms, flops=flops)
+    prd = torch.randn(Bd, 1, ld, device=dev, dtype=bf) * 0.3
+    at = torch.full((Bd,), T, dtype=torch.int32, device=dev)
+    ms = timer(lambda: rt.retention_scan(prd, offs, dec, st, at, Hr, Dk, Dvr, Dk ** -0.5, rope=rrope), steps, warmup)
+    row("retention, one token (state read + written)", "decode attention", ms, nbytes=8.0 * Dk * Dvr * Hr * Bd)
+    ms = timer(lambda: ml.mlstm_scan(prd, offs, gi[:Bd], gf[:Bd], mst, at, Hr, Dk, Dvr, Dk ** -0.5), steps, warmup)
+    row("matrix-memory scan, one token (the like kernel)", "decode attention", ms, nbytes=8.0 * Dk * Dvr * Hr * Bd)
+    o = torch.randn(N, Hr, Dvr, device=dev)
+    ms = timer(lambda: ml.head_norm_gate(o, pr.view(N, ld), 2 * Hr * Dk + Hr * Dvr, Hr, Dvr, None, 1e-6, True, bf,
+                                         gate_act="silu"), steps, warmup)
+    row("unit head norm * silu gate", "norm", ms, nbytes=float(N * Hr * Dvr * (4 + 2 + 2)))
+    del pr, o
+    # the stream update next to the gated residual of the parallel-residual family
+    St = VUFASUN_STREAMS
+    xs = torch.randn(N, St, W, device=dev)
+    y1, y2 = torch.randn(N, W, device=dev, dtype=bf), torch.randn(N, W, device=dev, dtype=bf)
+    mix, ow, iw = torch.eye(St, device=dev), torch.ones(St, device=dev), torch.ones(St, device=dev)
+    wn, wa_, wb = torch.ones(W, device=dev), torch.ones(W, device=dev), torch.ones(W, device=dev)
+    ms = timer(lambda: hc_ops.hc_step(xs, y1, mix, ow, iw, wn, 1e-6, bf), steps, warmup)
+    row(f"stream write + mixing + next read and norm ({St} streams)", "norm", ms, nbytes=float(N * W * (8 * St + 2 + 2)))
+    ms = timer(lambda: hc_ops.hc_step(xs, y1, mix, ow, iw, wn, 1e-6, bf, y2=y2, branch_w=(wa_, wb)), steps, warmup)
+    row(f"the same with the mean of two normed branches ({St} streams)", "norm", ms, nbytes=float(N * W * (8 * St + 4 + 2)))
+    x32 = torch.randn(N, W, device=dev)
+    gate = torch.randn(N, 2 * W, device=dev, dtype=bf)
+    vecs = [torch.randn(W, device=dev) for _ in range(5)]
+    wnext = torch.ones(1, device=dev)
+    ms = timer(lambda: norm_ops.gated_residual_norm_(x32, y1, y2, vecs[0], gate, (0, W), vecs[1], vecs[2], vecs[3], vecs[4],
+                                                     wnext, 1e-6, bf), steps, warmup)
+    row("gated residual of both sublayers + layer scale + next norm (the like kernel)", "norm", ms,
+        nbytes=float(N * W * (4 + 4 + 2 + 2 + 4 + 2)))
+    del xs, x32, gate
+    F = (2 * s["ff"] // 3 + 127) // 128 * 128
+    src = torch.randn(N, 2 * F, device=dev, dtype=bf)
+    ms = timer(lambda: moe_sparse.glu_bias(src, 0, F, F, act="gelu_tanh"), steps, warmup)
+    row("gelu_tanh(gate) * up from the fused projection", "activation", ms, nbytes=2.0 * N * 3 * F)
+    gb, ub = torch.zeros(F, device=dev), torch.zeros(F, device=dev)
+    ms = timer(lambda: moe_sparse.glu_bias(src, 0, F, F, gb, ub), steps, warmup)
+    row("silu(gate + b) * (up + b) from the fused projection (the like kernel)", "activation", ms, nbytes=2.0 * N * 3 * F)
+    return rows
+
+
+def run_retention(steps: int = 10, warmup: int = 3, device=None, sizes=None) -> dict:
+    dev = device or torch.device("cuda", torch.cuda.current_device())
+    before = _lib.kernel_launches()
+    out = {"metric": "Vufasun vs Gogalix, serving throughput at equal layer sizes", "dtype": "bf16",
+           "data": "synthetic token ids, random-init weights", "steps": steps, "warmup": max(warmup, 3),
+           "l2": "192 MB written between timed runs", "peaks": peaks(), "cases": [], "kernels": {}}
+    for s in (sizes or HYBRID_SIZES):
+        out["cases"].append(retention_serve_case(s, steps, warmup, dev))
+        out["kernels"][s["name"]] = retention_kernel_cases(s, steps, warmup, dev)
+    out["gpu_launches"] = _lib.kernel_launches() - before
+    return out

@@ -22,7 +22,7 @@ from . import _lib
 
 GROUP = "retention_serving"
 CHUNK = 64
-_SMEM_LIMIT = 200 * 1024
+_SMEM_LIMIT = 220 * 1024
 
 
 def _code(dtype: torch.dtype) -> int:
@@ -40,9 +40,11 @@ def _i32(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
 
 
 def chunkwise_applies(dim: int, vdim: int) -> bool:
-    """The chunk-wise kernels keep a chunk's q, k, v and scores (and a head's state) in shared memory."""
-    local = (2 * CHUNK * (dim + 1) + CHUNK * (CHUNK + 1) + CHUNK * vdim) * 4
-    cross = (dim * vdim + CHUNK * dim) * 4
+    """The chunk-wise kernels keep a chunk's q, k, scores and a tile of at most 128 value columns (and that tile of a
+    head's state) in shared memory."""
+    vt = min(128, (vdim + 3) // 4 * 4)
+    local = (2 * CHUNK * (dim + 1) + CHUNK * (CHUNK + 1) + CHUNK * vt) * 4
+    cross = (dim * vt + CHUNK * dim) * 4
     return max(local, cross) <= _SMEM_LIMIT
 
 

@@ -116,6 +116,8 @@ def qk_norm_cache_write(qkv: torch.Tensor, cache_k: Optional[torch.Tensor], cach
         qw = q_weight.float().contiguous() if q_weight is not None else None
         kw = k_weight.float().contiguous() if k_weight is not None else None
         cos, sin = rope if rope is not None else (None, None)
+        # scratch of the whole-projection statistics (1 / rms of all query heads, of all key heads, per row)
+        stat = torch.empty(B * T, 2, dtype=torch.float32, device=qkv.device) if (whole_norm and normalize) else None
         rc = L.nxd_qk_prep_cache_write(_c.c_int(_code(qkv.dtype)), _lib.ptr(qkv), _c.c_longlong(ld), _lib.ptr(q),
                                        _lib.ptr(ck), _lib.ptr(cv), *cargs, _lib.ptr(qs), _lib.ptr(nn_), _lib.ptr(sid),
                                        _c.c_int(B), _c.c_int(T), _c.c_int(heads), _c.c_int(kv_heads), _c.c_int(dim),
@@ -124,7 +126,7 @@ def qk_norm_cache_write(qkv: torch.Tensor, cache_k: Optional[torch.Tensor], cach
                                        _lib.ptr(cos), _lib.ptr(sin), _c.c_int(2 * cos.shape[1] if cos is not None else 0),
                                        _c.c_int(int(value_from_key)), _c.c_int(gv),
                                        _c.c_int(int(rope_layout == "halves")), _c.c_int(int(whole_norm)),
-                                       _lib.stream_ptr())
+                                       _lib.ptr(stat), _lib.stream_ptr())
         _lib.check(rc, "nxd_qk_prep_cache_write", L)
         return q
 
