@@ -85,7 +85,7 @@ ODD = config(layers=[
 PLAIN = config(layers=[layer("attention"), layer("parallel", mlp=None)], streams=None, loop=None)   # no stream weights at all
 
 
-def build(cfg, dev, dt, lines=4, seq_len=96, seed=0, paged=False, pages=None, page_size=8, sd=None):
+def build(cfg, dev, dt, lines=4, seq_len=96, seed=1, paged=False, pages=None, page_size=8, sd=None):
     sd = sd if sd is not None else O.random_weights(cfg, seed)
     vc = VufasunConfig.from_dict(cfg, torch_dtype=dt).with_checkpoint_shapes(sd)
     ic = InferenceConfig(batch_size=lines, max_batch_size=lines, max_context_length=seq_len, seq_len=seq_len,
