@@ -415,7 +415,9 @@ class VufasunInferenceModel(KVCacheInferenceMixin, VufasunForCausalLM):
       * ONE matrix product of the mixer's input gives all its projections (``layer.in_proj``, parts at
         ``layer.columns``); the kernels read their part in place;
       * softmax attention: whole-projection norm (left branch of a parallel layer) + "rotate half" rotation + cache write
-        in one kernel, then attention over the cache with the sink logit in the denominator (``attention`` layers);
+        in one kernel, then attention over the cache with the sink logit in the denominator (``attention`` layers); a
+        bf16 prompt from position 0 without a sink term and with equal key / value sizes of 64 or 128 runs on the tcgen05
+        flash-attention kernel instead;
       * retention: rotation, key scale and the recurrence on the line's fp32 state in one kernel (token by token, or in
         chunks of 64 tokens for long steps), then unit RMS per head * ``silu`` gate;
       * a parallel layer hands both branch outputs to the stream kernel, which norms and averages them;
@@ -425,6 +427,7 @@ class VufasunInferenceModel(KVCacheInferenceMixin, VufasunForCausalLM):
 
     supports_prefill_at_offset = True
     CHUNKWISE_MIN_TOKENS = 64            # shorter steps walk the recurrence token by token
+    TC_PREFILL_MIN_TOKENS = 128          # shorter steps stay on the cache-reading attention kernels
 
     def __init__(self, config: VufasunConfig, inference_config: Optional[InferenceConfig] = None, device=None):
         VufasunForCausalLM.__init__(self, config, device=device)
@@ -503,6 +506,14 @@ class VufasunInferenceModel(KVCacheInferenceMixin, VufasunForCausalLM):
         if T == 1:
             o = wa_ops.window_attention_decode(q[:, 0], ck, cv, q_start, m.scale, seq_ids=seq_ids, sinks=mixer.sink,
                                                **paged)
+        elif (mixer.sink is None and T >= self.TC_PREFILL_MIN_TOKENS and not self._step_past_context
+              and not self.kv_cache.paged and wa_ops.tc_prefill_applies(qkv, m.dim, m.vdim, big.shape[-1])):
+            # prompts from position 0 without a sink term on the tcgen05 flash-attention kernel: K comes back from the cache
+            # rows just written (normed and rotated), V is the value columns of the projection output, read in place
+            lines = seq_ids.long() if seq_ids is not None else torch.arange(B, device=big.device)
+            vx = qkv[..., (m.heads + m.kv_heads) * m.dim:].reshape(B, T, m.kv_heads, m.vdim)
+            o = attn_ops.flash_attn_func(q.permute(0, 2, 1, 3), ck[lines, :, :T], vx.permute(0, 2, 1, 3),
+                                         softmax_scale=m.scale, causal=True).permute(0, 2, 1, 3)
         else:
             o = wa_ops.window_attention_prefill(q, ck, cv, q_start, m.scale, n_new=n_new, seq_ids=seq_ids,
                                                 sinks=mixer.sink, **paged)

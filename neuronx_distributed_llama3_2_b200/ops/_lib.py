@@ -63,9 +63,10 @@ GROUPS["delta_serving"] = ["window_attention.cu", "post_norm.cu", "moe_sparse.cu
 
 # the retention hybrids (softmax attention with sinks next to fixed-decay linear attention, several residual streams,
 # dense and sparse gated feed-forward): attention over the cache, sparse MoE, the head norm / gate of recurrent outputs,
-# their own two sources and the GEMM kernels behind the linear layers
+# their own two sources, the GEMM kernels behind the linear layers and the tcgen05 flash attention of sink-free prompts
 GROUPS["retention_serving"] = ["window_attention.cu", "moe_sparse.cu", "mlstm.cu", "retention.cu", "hyper_connection.cu",
-                               "runtime.cu", "gemm_tcgen05.cu", "gemm_smallm.cu", "fused_gemm_ar.cu", "tma_host.cu"]
+                               "runtime.cu", "gemm_tcgen05.cu", "gemm_smallm.cu", "fused_gemm_ar.cu", "tma_host.cu",
+                               "flash_attn_tc.cu", "attn_tc_host.cu"]
 
 # sources whose fp32 state is carried over thousands of steps: no approximate exp / tanh / division
 PRECISE_SOURCES = {"mlstm.cu", "delta_rule.cu", "retention.cu", "hyper_connection.cu"}

@@ -589,7 +589,8 @@ def test_a_token_far_back_lives_on_in_the_retention_state(dev, dt):
 @case
 def test_sizes_of_the_tensor_core_and_wide_register_kernels_through_the_model(dev, dt):
     """Key sizes 64 / 128 (the attention's tensor-core kernels in bf16, the widest register slices of the recurrence),
-    grouped heads, four streams, prompts of 70 and 100 tokens in one batch, a portion at an offset, decoding."""
+    grouped heads, four streams, prompts of 70 and 130 tokens in one batch (in bf16 the sink-free left branch then runs on
+    the tcgen05 flash-attention kernel, next to a padded row), a portion at an offset, decoding."""
     big_left = dict(heads=2, kv_heads=1, dim=128, vdim=128, scale=0.09, rot={"base": 1e4, "dims": 64})
     cfg = config(layers=[layer("parallel", left=big_left, right=dict(heads=2, dim=128, vdim=64, decay=[0.98, 0.999],
                                                                       rot={"base": 1e4, "dims": 128}), mlp=None),
@@ -599,12 +600,12 @@ def test_sizes_of_the_tensor_core_and_wide_register_kernels_through_the_model(de
     model, sd = build(cfg, dev, dt, lines=2, seq_len=200)
     a, b = tokens_of(cfg, 170, 51), tokens_of(cfg, 80, 52)
     ra, rb = O.forward(cfg, sd, a), O.forward(cfg, sd, b)
-    steps = [([{"id": "a", "tokens": a[:100], "want": [0, 47, 48, 99]}, {"id": "b", "tokens": b[:70], "want": [69]}], []),
-             ([{"id": "a", "tokens": a[100:160], "want": [0, 59]}], [])]
+    steps = [([{"id": "a", "tokens": a[:130], "want": [0, 47, 48, 129]}, {"id": "b", "tokens": b[:70], "want": [69]}], []),
+             ([{"id": "a", "tokens": a[130:160], "want": [0, 29]}], [])]
     steps += [([{"id": "a", "tokens": [a[160 + s]], "want": [0]}, {"id": "b", "tokens": [b[70 + s]], "want": [0]}], [])
               for s in range(6)]
     got = replay(model, steps)
-    check_rows(got["a"], ra, [0, 47, 48, 99, 100, 159] + list(range(160, 166)), dt, strict=1e-3, risky=O.close_calls(cfg, sd, a))
+    check_rows(got["a"], ra, [0, 47, 48, 129, 130, 159] + list(range(160, 166)), dt, strict=1e-3, risky=O.close_calls(cfg, sd, a))
     check_rows(got["b"], rb, [69] + list(range(70, 76)), dt, strict=1e-3, risky=O.close_calls(cfg, sd, b))
 
 
