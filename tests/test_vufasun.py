@@ -84,6 +84,18 @@ ODD = config(layers=[
 
 PLAIN = config(layers=[layer("attention"), layer("parallel", mlp=None)], streams=None, loop=None)   # no stream weights at all
 
+# five streams (more than the vectorised stream kernel takes), a middle range run four times, a fast and a nearly lossless
+# decay side by side, rotation over half of a head that is no power of two, a strongly slowed frequency band
+FIVE = config(layers=[
+    layer("attention", heads=3, kv_heads=1, dim=24, vdim=40, scale=0.3, rot={"base": 1e4, "dims": 8},
+          mlp={"kind": "moe", "expert": {"ff": 48}, "router": {"experts": 3, "top": 3}, "shared": {"ff": 40}}),
+    layer("attention", heads=2, kv_heads=2, dim=80, vdim=16, scale=0.11, rot={"base": 1e5, "dims": 80}, mlp={"kind": "dense", "ff": 120}),
+    layer("parallel", mlp={"kind": "moe", "expert": {"ff": 24}, "router": {"experts": 5, "top": 4}, "shared": {"ff": 8}},
+          left=dict(heads=6, kv_heads=2, dim=16, vdim=16, scale=0.25,
+                    rot={"base": 1e4, "dims": 16, "scaling": {"factor": 16.0, "low": 2.0, "high": 3.0, "original": 64}}),
+          right=dict(heads=3, dim=24, vdim=40, decay=[0.5, 0.9, 0.99999], rot={"base": 5e4, "dims": 12})),
+], vocab=130, width=72, streams=5, loop=(1, 3, 4))
+
 
 def build(cfg, dev, dt, lines=4, seq_len=96, seed=1, paged=False, pages=None, page_size=8, sd=None):
     sd = sd if sd is not None else O.random_weights(cfg, seed)
@@ -438,7 +450,7 @@ def test_checkpoint_names_round_trip_and_the_fused_projection_layout():
 
 # ---- the model through the framework -----------------------------------------------------------------------------------
 @case
-@pytest.mark.parametrize("cfg", [config(), ODD, PLAIN], ids=["mixed", "odd", "plain"])
+@pytest.mark.parametrize("cfg", [config(), ODD, PLAIN, FIVE], ids=["mixed", "odd", "plain", "five"])
 def test_prefill_matches_oracle_and_token_by_token_decoding(dev, dt, cfg):
     toks = tokens_of(cfg, 45, 1)
     model, sd = build(cfg, dev, dt, seed=2)                   # a seed without near ties among the router scores
@@ -452,8 +464,9 @@ def test_prefill_matches_oracle_and_token_by_token_decoding(dev, dt, cfg):
     risky = O.close_calls(cfg, sd, toks)
     check_rows(whole, ref, want, dt, risky=risky)
     assert len(seen) == len(streams) == len(O.layer_runs(cfg))
+    rows = [p for p in want if dt == torch.float32 or p not in risky]      # bf16 may swap an expert at a nearly tied score
     for got, exp in zip(seen, streams):                       # the sum of the streams after every layer run
-        assert float((got[0] - exp).abs().max()) <= (2e-3 if dt == torch.float32 else 0.08 * float(exp.abs().max()) + 0.5)
+        assert float((got[0] - exp)[rows].abs().max()) <= (2e-3 if dt == torch.float32 else 0.08 * float(exp.abs().max()) + 0.5)
     steps = [([{"id": "b", "tokens": toks[:1], "want": [0]}], [])]
     steps += [([{"id": "b", "tokens": [t], "want": [0]}], []) for t in toks[1:]]
     check_rows(replay(model, steps)["b"], ref, want, dt, risky=risky)
